@@ -130,6 +130,10 @@ class Model:
         x = self.embedding.forward(step.token_ids)
         if self.position is not None:
             self.position.add_to_embedding(x, step)
+        if self.spec.keep_embedded:       # a second gather, not a copy: the stream itself is rewritten in place
+            step.embedded = self.embedding.forward(step.token_ids)
+            if self.position is not None:
+                self.position.add_to_embedding(step.embedded, step)
         carry = None                  # rows a layer's last product prepared for the next layer's first norm
         for stop, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]

@@ -54,6 +54,7 @@ class StepBatch:
     host: Optional[dict] = None       # the same numbers on the host, for parts that plan launches
     fixed_qblocks: Optional[Dict[int, tuple]] = None   # a captured prompt step: its query blocks, padded lists
     sizes_seen: Optional[set] = None  # when set: the block sizes `query_blocks` was asked for are noted here
+    embedded: Optional[torch.Tensor] = None   # float32 [T, hidden]: the embedded tokens, for models that re-read them
     _qblocks: Dict[int, tuple] = field(default_factory=dict)
     _rotation: Dict[object, torch.Tensor] = field(default_factory=dict)
 

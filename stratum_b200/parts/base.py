@@ -165,6 +165,15 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamOp(Part):
+    """Something that acts on the residual stream as a whole, between layers (not a sublayer with a residual
+    connection): forward rewrites x in place.  step.embedded holds the embedded tokens of the step for parts that
+    read them (a model whose spec sets `keep_embedded`)."""
+
+    def forward(self, x: torch.Tensor, step) -> None:
+        raise NotImplementedError
+
+
 class Embedding(Part):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         """int32 [T] -> float32 [T, hidden]."""

@@ -104,3 +104,66 @@ class OutputNormResidual(Arrangement):
         copy = rt.empty(*x.shape) if rounded and isinstance(hand_to, RoundedRows) else None
         norm_b.add_normed(y, x, True, copy)
         return copy
+
+
+@register_part("arrangement", "sandwich_norm_residual")
+class SandwichNormResidual(Arrangement):
+    """x += post_a(mixer(pre_a(x))); x += post_b(feed_forward(pre_b(x))): a norm on either side of every sublayer.  A
+    constant factor on a sublayer's contribution (a residual multiplier) belongs to the norm behind it (its `scale`).
+    The norm behind a sublayer adds into the stream and, where the next thing to read the stream is a norm it can
+    make from the row it has just written (the one in front of the next sublayer, also across a layer's border), hands
+    that norm's output on, so the stream is passed over once between two sublayers."""
+    replays_prompts = True
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "mixer_out_norm": "norm",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_out_norm": "norm"}
+    optional = ("feed_forward_norm", "feed_forward", "feed_forward_out_norm")
+    carries = True
+
+    def accepts_carry(self, layer):
+        return layer.part("mixer_norm")
+
+    @staticmethod
+    def _run(part, xn, y, step, cache=None) -> None:
+        args = (xn, y, step) if cache is None else (xn, y, step, cache)
+        if part.stores_output:
+            part.forward(*args, store=True)
+        else:
+            y.zero_()
+            part.forward(*args)
+
+    @staticmethod
+    def _behind(norm, y, x, then):
+        """x += norm(y); the output of `then` on the new rows if the norm made it, else None."""
+        try:
+            return norm.add_normed(y, x, True, then=then) if then is not None else norm.add_normed(y, x, True)
+        except TypeError:                  # a norm whose form behind a sublayer knows nothing of the norm after it
+            norm.add_normed(y, x, True)
+            return None
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache, carry=None, hand_to=None):
+        pre_a, mixer, post_a = layer.part("mixer_norm"), layer.part("mixer"), layer.part("mixer_out_norm")
+        pre_b, ff, post_b = (layer.part("feed_forward_norm"), layer.part("feed_forward"),
+                             layer.part("feed_forward_out_norm"))
+        rt = mixer.runtime
+        xn = carry if isinstance(carry, torch.Tensor) else pre_a.forward(x)
+        y = rt.empty(*x.shape, dtype=torch.float32)
+        self._run(mixer, xn, y, step, cache)
+        if ff is None or pre_b is None or post_b is None:
+            return self._behind(post_a, y, x, hand_to)
+        xn = self._behind(post_a, y, x, pre_b)
+        if xn is None:
+            xn = pre_b.forward(x)
+        self._run(ff, xn, y, step)
+        return self._behind(post_b, y, x, hand_to)
+
+
+@register_part("arrangement", "stream_op")
+class StreamOpLayer(Arrangement):
+    """A stop of the schedule that is no decoder layer: one part (`op`, a stream_op) rewrites the residual stream in
+    place (a projection at the head of a pass over looped layers, say).  It keeps nothing per sequence."""
+    replays_prompts = True
+    slots = {"op": "stream_op"}
+    cache_owner = None
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
+        layer.part("op").forward(x, step)

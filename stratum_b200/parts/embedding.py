@@ -52,8 +52,9 @@ class TokenEmbedding(Embedding):
 
 @register_part("head", "linear_head")
 class LinearHead(Head):
-    """params: vocab, hidden, tied (the file may leave the matrix out), prefix (e.g. "lm_head."; the matrix is
-    prefix + "weight"), or tensor (the matrix's whole name)."""
+    """params: vocab, hidden, tied (the file may leave the matrix out: the embedding table then serves), prefix (e.g.
+    "lm_head."; the matrix is prefix + "weight"), or tensor (the matrix's whole name); own_matrix (default true;
+    false: the head has no tensor of its own and is always the embedding table)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
@@ -61,13 +62,16 @@ class LinearHead(Head):
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.tied = bool(spec.get("tied", False))
         self.name = spec.get("tensor") or self.prefix + "weight"
+        self.own_matrix = bool(spec.get("own_matrix", True))
         self.proj: Optional[Linear] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
+        if not self.own_matrix:
+            return {}
         return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied)}
 
     def bind_with_embedding(self, weights: Mapping[str, torch.Tensor], table: torch.Tensor) -> None:
-        w = weights.get(self.name)
+        w = weights.get(self.name) if self.own_matrix else None
         self.proj = Linear(self.runtime, w if w is not None else table)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:

@@ -61,6 +61,53 @@ class RMSNorm(Norm):
         K.rmsnorm_heads(x, first_col, n_heads, head_dim, self.gain, self.eps)
 
 
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean x) / sqrt(var x + eps) * w, a weight and no bias (var: the mean of the squared deviations).
+    params: size, eps, tensor (the weight's whole name) or prefix (then prefix + "weight"), scale (a constant factor
+    on the result, folded into the weight when it is bound: a layer's residual multiplier rides here at no cost)."""
+    replays_prompts = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.tensor = spec.get("tensor")
+        self.scale = float(spec.get("scale", 1.0))
+        self.gain: Optional[torch.Tensor] = None
+
+    @property
+    def name(self) -> str:
+        return self.tensor or self.prefix + "weight"
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.size,), role="vector", init="ones")}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        w = weights[self.name]
+        self.gain = (w * self.scale).contiguous() if self.scale != 1.0 else w
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = self.runtime.empty(n, self.size)
+        K.layernorm(x, self.gain, self.eps, out, rows)
+        return out
+
+    def add_normed(self, y: torch.Tensor, residual: torch.Tensor, accumulate: bool = True,
+                   copy: Optional[torch.Tensor] = None, then: Optional[Norm] = None) -> Optional[torch.Tensor]:
+        """residual (+)= norm(y).  then: the norm that the next sublayer reads the stream through; where that is a
+        layer norm of this size, its output (compute dtype) is made by the same kernel, from the row it has just
+        written, and returned; otherwise None comes back and that norm runs by itself."""
+        if copy is not None:
+            raise ValueError("layernorm: the form behind a sublayer leaves no rounded copy of the stream")
+        if isinstance(then, LayerNorm) and then.size == self.size:
+            out = self.runtime.empty(*residual.shape)
+            K.layernorm_into_residual(y, self.gain, self.eps, residual, accumulate, then.gain, then.eps, out)
+            return out
+        K.layernorm_into_residual(y, self.gain, self.eps, residual, accumulate)
+        return None
+
+
 @register_part("norm", "dynamic_tanh")
 class DynamicTanh(Norm):
     """params: size, name (the weight's tensor name; the bias is name + ".b", the scalar name + ".alpha")."""

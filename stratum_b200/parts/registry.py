@@ -1,7 +1,7 @@
 """One registry per category of part: name -> class.
 
 A part registers itself under a category ("mixer", "feed_forward", "norm",
-"position", "arrangement", "embedding", "head").  A model spec refers to
+"position", "arrangement", "embedding", "head", "stream_op").  A model spec refers to
 parts only by these names, so a new part needs no change to the engine: define
 the class, register it, name it in a spec.  The reference registers whole
 architectures the same way, by name in a table
@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Type
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "arrangement", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "arrangement", "embedding", "head", "stream_op")
 
 _REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in CATEGORIES}
 

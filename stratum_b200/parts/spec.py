@@ -66,6 +66,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     position: Optional[PartSpec] = None     # an encoding that acts on the embedded tokens (absolute positions)
+    keep_embedded: bool = False             # the embedded tokens stay at hand for the whole step (StepBatch.embedded)
 
     def check(self) -> None:
         n = len(self.layers)
