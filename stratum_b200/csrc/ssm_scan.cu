@@ -1,0 +1,314 @@
+// A selective state-space mixer (the scalar-decay form): per head one matrix S [n_state][vdim] in float32.
+//
+// Per token, from the float32 sums of the fused input projection (row = [z | x | B | C | dt]: inner = n_heads * vdim,
+// inner, n_groups * n_state, n_groups * n_state, n_heads):
+//   prep      x, B and C (the `channels` = inner + 2 n_groups n_state columns from column inner on) pass a short causal
+//             convolution over time with a bias (taps per channel, the last tap is the current token's; the taps - 1
+//             inputs before a step's first token come from the sequence's state, zeros before the sequence's start) and
+//             silu;  dt <- softplus(dt + dt_bias), not clamped;  decay = exp(-exp(A_log) dt).
+//   recur     per head h (its B and C are those of group h / (n_heads / n_groups)), token after token:
+//             S <- decay S + dt B x^T;   y = S^T C + D x.   The convolution's tail is moved on as well.
+//   finish    y <- y silu(z); the row is cut into `norm_groups` equal parts, each divided by its own root mean square
+//             (eps inside the root); times the gain; rounded to the compute dtype for the output product.
+// All of it is float32 whatever the compute dtype.
+//
+// Every entry of S follows a recurrence of its own, so the work is independent across sequences, heads, columns and
+// rows of S and sequential only in time.  A block owns (sequence, head, a tile of columns), a thread 16 rows of one
+// column; the column's read-out is added over neighbouring lanes by shuffles in a fixed order.  The tokens' B, C, x,
+// dt and decay come through a double buffer in shared memory (cp.async).  Nothing depends on how a sequence's
+// tokens are cut into steps, nor on the other sequences of a step.
+#include <math.h>
+
+#include "common.cuh"
+
+struct SsmScan {
+  const float* proj;        // [tokens][ld]
+  const float* conv_w;      // [channels][taps]
+  const float* conv_b;      // [channels]
+  const float* a_log;       // [n_heads]
+  const float* dt_bias;     // [n_heads]
+  const float* d_skip;      // [n_heads]
+  const float* gain;        // [inner]
+  float* act;               // [tokens][lda]: x | B | C after prep, then dt [n_heads], decay [n_heads]
+  float* y_raw;             // [tokens][inner]
+  void* out;                // [tokens][ldo] compute dtype
+  float* state;             // [slots][state_stride]: S^T [n_heads][vdim][n_state], then the tail [taps - 1][channels]
+  const int* token_pos;
+  const int* token_seq;
+  const int* seq_start;     // [seqs + 1]
+  const int* seq_slot;      // [seqs]
+  int ld, lda, ldo, n_tokens, n_seqs;
+  int n_heads, vdim, n_state, n_groups, taps, norm_groups;
+  int state_stride, write_state;
+  float eps;
+};
+
+__device__ __forceinline__ float ss_silu(float z) { return z / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------- prep: one block per token
+#define SS_PREP_THREADS 256
+__global__ void __launch_bounds__(SS_PREP_THREADS) ssm_prep_kernel(const SsmScan P) {
+  pdl_trigger();
+  pdl_wait();                // the projection and the state are the work of kernels before this one: ld_fresh
+  const int t = blockIdx.x;
+  const int inner = P.n_heads * P.vdim, C = inner + 2 * P.n_groups * P.n_state;
+  const int seq = P.token_seq[t], pos = P.token_pos[t];
+  int in_step = 0;           // tokens of this sequence that the step brought before this one
+  const float* tail = nullptr;
+  if (seq >= 0) {
+    in_step = t - P.seq_start[seq];
+    tail = P.state + (size_t)P.seq_slot[seq] * P.state_stride + (size_t)inner * P.n_state;
+  }
+  float* out = P.act + (size_t)t * P.lda;
+  const int n = P.taps;
+  for (int c = threadIdx.x; c < C; c += SS_PREP_THREADS) {
+    const float* w = P.conv_w + (size_t)c * n;
+    float acc = P.conv_b[c];
+    for (int i = n - 1; i >= 0; i--) {               // oldest input first: one fixed order
+      float x = 0.f;
+      if (i <= in_step) x = ld_fresh(P.proj + (size_t)(t - i) * P.ld + inner + c);
+      else if (tail && pos - i >= 0) x = ld_fresh(tail + (size_t)(n - 1 - (i - in_step)) * C + c);
+      acc = fmaf(w[n - 1 - i], x, acc);
+    }
+    out[c] = ss_silu(acc);
+  }
+  for (int h = threadIdx.x; h < P.n_heads; h += SS_PREP_THREADS) {
+    const float z = ld_fresh(P.proj + (size_t)t * P.ld + inner + C + h) + P.dt_bias[h];
+    const float dt = z > 20.f ? z : log1pf(expf(z));
+    out[C + h] = dt;
+    out[C + P.n_heads + h] = expf(-expf(P.a_log[h]) * dt);
+  }
+}
+
+// ---------------------------------------------------------------- the recurrence
+#define SS_THREADS 128
+#define SS_ROWS 16            // rows of a column of S that a lane holds
+#define SS_MAX_CHUNK 16       // tokens staged in shared memory at a time, at most
+
+__device__ __forceinline__ void ss_copy4(float* dst_shared, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void ss_copy16(float* dst_shared, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void ss_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ss_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// The state of a head lies in memory column by column (S^T: [vdim][n_state]), so the rows a thread holds are
+// contiguous.  A column is spread over L lanes of SS_ROWS rows each (n_state <= SS_ROWS * L).
+template <int L>
+__global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) {
+  constexpr int ROWS = SS_ROWS;
+  constexpr int COLS = SS_THREADS / L;
+  constexpr int PITCH = 20;   // floats between two lanes' stretches of B and C: 16-byte aligned, banks spread
+  constexpr int BC = L * PITCH;
+  constexpr int FIT = 2048 / BC;
+  constexpr int CHUNK = FIT < 4 ? 4 : (FIT > SS_MAX_CHUNK ? SS_MAX_CHUNK : (FIT & ~3));
+  __shared__ __align__(16) float bc_s[2][CHUNK][2][BC];
+  __shared__ float x_s[2][CHUNK][COLS];
+  __shared__ float dd_s[2][CHUNK][2];                // dt, decay
+  pdl_trigger();             // (launched the ordinary way itself: it starts when prep is done)
+  const int seq = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+  const int r0 = P.seq_start[seq], r1 = P.seq_start[seq + 1];
+  if (r0 >= r1) return;
+  const int N = P.n_state, V = P.vdim, inner = P.n_heads * V, GN = P.n_groups * N, C = inner + 2 * GN;
+  const int part = threadIdx.x % L, col = threadIdx.x / L;
+  const int j = tile * COLS + col;
+  const bool live = j < V;
+  if (P.token_seq[r0] < 0) {                         // rows of no sequence: nothing is kept, the output is zero
+    if (part == 0 && live)
+      for (int r = r0; r < r1; r++) P.y_raw[(size_t)r * inner + (size_t)h * V + j] = 0.f;
+    return;
+  }
+  float* slot = P.state + (size_t)P.seq_slot[seq] * P.state_stride;
+
+  // the convolution's tail moves on by this step's tokens: the blocks of a sequence share the channels, a thread
+  // takes a channel through time in order, so that an entry is read before it is overwritten
+  if (P.write_state && P.taps > 1) {
+    float* tail = slot + (size_t)inner * N;
+    const int keep = P.taps - 1, n_new = r1 - r0;
+    const int n_blocks = gridDim.x * gridDim.y, me = blockIdx.y * gridDim.x + blockIdx.x;
+    const int per = (C + n_blocks - 1) / n_blocks;
+    const int c_end = min(C, (me + 1) * per);
+    for (int c = me * per + threadIdx.x; c < c_end; c += SS_THREADS)
+      for (int i = 0; i < keep; i++) {
+        const int back = keep - i;                   // this entry is the input `back` tokens before the next one
+        tail[(size_t)i * C + c] = back <= n_new ? P.proj[(size_t)(r1 - back) * P.ld + inner + c]
+                                                : tail[(size_t)(i + n_new) * C + c];
+      }
+  }
+
+  const int g = h / (P.n_heads / P.n_groups);
+  const float d_skip = P.d_skip[h];
+  float* Sg = slot + ((size_t)h * V + (live ? j : 0)) * N + part * ROWS;
+  const bool vec = N % 4 == 0 && (P.state_stride % 4) == 0 && (((uintptr_t)P.state) & 15) == 0;
+  float2 S[ROWS / 2];
+#pragma unroll
+  for (int i = 0; i < ROWS; i += 4) {
+    const int d = part * ROWS + i;
+    if (live && vec && d + 3 < N) {
+      const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
+      S[i / 2] = make_float2(v4.x, v4.y); S[i / 2 + 1] = make_float2(v4.z, v4.w);
+    } else {
+      float e[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) e[u] = (live && d + u < N) ? Sg[i + u] : 0.f;
+      S[i / 2] = make_float2(e[0], e[1]); S[i / 2 + 1] = make_float2(e[2], e[3]);
+    }
+  }
+  if (N != ROWS * L) {       // the rows beyond n_state in the staging buffers stay zero: nothing below writes them
+    for (int i = threadIdx.x; i < 2 * CHUNK * 2 * BC; i += SS_THREADS) (&bc_s[0][0][0][0])[i] = 0.f;
+    __syncthreads();
+  }
+
+  const bool vec_act = N % 4 == 0 && P.lda % 4 == 0 && inner % 4 == 0 && (((uintptr_t)P.act) & 15) == 0;
+  auto stage = [&](int buf, int c0) {                // ask for the tokens c0 .. of this sequence
+    const int n_here = min(CHUNK, r1 - c0);
+    for (int tok = 0; tok < n_here; tok++) {
+      const float* a = P.act + (size_t)(c0 + tok) * P.lda + inner + (size_t)g * N;
+      if (vec_act) {
+        for (int d = 4 * threadIdx.x; d < 2 * N; d += 4 * SS_THREADS) {          // B, then C
+          const int which = d >= N, dd = d - which * N;
+          ss_copy16(&bc_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + which * GN + dd);
+        }
+      } else {
+        for (int d = threadIdx.x; d < 2 * N; d += SS_THREADS) {
+          const int which = d >= N, dd = d - which * N;
+          ss_copy4(&bc_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + which * GN + dd);
+        }
+      }
+    }
+    for (int i = threadIdx.x; i < n_here * COLS; i += SS_THREADS) {
+      const int tok = i / COLS, cc = i - tok * COLS, jj = tile * COLS + cc;
+      if (jj < V) ss_copy4(&x_s[buf][tok][cc], P.act + (size_t)(c0 + tok) * P.lda + (size_t)h * V + jj);
+    }
+    if (threadIdx.x < n_here * 2) {
+      const int tok = threadIdx.x >> 1, which = threadIdx.x & 1;                 // 0 = dt, 1 = decay
+      ss_copy4(&dd_s[buf][tok][which], P.act + (size_t)(c0 + tok) * P.lda + C + which * P.n_heads + h);
+    }
+    ss_commit();
+  };
+
+  stage(0, r0);
+  int buf = 0;
+  for (int c0 = r0; c0 < r1; c0 += CHUNK, buf ^= 1) {
+    ss_wait_all();
+    __syncthreads();                                 // this chunk has landed, and the other buffer is free again
+    if (c0 + CHUNK < r1) stage(buf ^ 1, c0 + CHUNK);
+    const int n_here = min(CHUNK, r1 - c0);
+    float* y_row = P.y_raw + (size_t)c0 * inner + (size_t)h * V + (live ? j : 0);
+#pragma unroll 2
+    for (int tok = 0; tok < n_here; tok++, y_row += inner) {
+      const float4* bb = reinterpret_cast<const float4*>(&bc_s[buf][tok][0][part * PITCH]);
+      const float4* cc = reinterpret_cast<const float4*>(&bc_s[buf][tok][1][part * PITCH]);
+      const float dt = dd_s[buf][tok][0], decay = dd_s[buf][tok][1];
+      const float xj = x_s[buf][tok][col];
+      const float dtx = dt * xj;
+      const float2 uu = make_float2(dtx, dtx), dk = make_float2(decay, decay);
+      float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+#pragma unroll
+      for (int i = 0; i < ROWS / 4; i++) {
+        const float4 b4 = bb[i], c4 = cc[i];
+        S[2 * i] = __ffma2_rn(make_float2(b4.x, b4.y), uu, __fmul2_rn(dk, S[2 * i]));
+        S[2 * i + 1] = __ffma2_rn(make_float2(b4.z, b4.w), uu, __fmul2_rn(dk, S[2 * i + 1]));
+        a0 = __ffma2_rn(S[2 * i], make_float2(c4.x, c4.y), a0);
+        a1 = __ffma2_rn(S[2 * i + 1], make_float2(c4.z, c4.w), a1);
+      }
+      const float2 s2 = __fadd2_rn(a0, a1);
+      float y = s2.x + s2.y;
+#pragma unroll
+      for (int o = 1; o < L; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (part == 0 && live) *y_row = fmaf(d_skip, xj, y);
+    }
+  }
+  if (P.write_state && live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; i += 4) {
+      const int d = part * ROWS + i;
+      const float e[4] = {S[i / 2].x, S[i / 2].y, S[i / 2 + 1].x, S[i / 2 + 1].y};
+      if (vec && d + 3 < N) {
+        *reinterpret_cast<float4*>(Sg + i) = make_float4(e[0], e[1], e[2], e[3]);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (d + u < N) Sg[i + u] = e[u];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- finish: one warp per (token, part of the row)
+template <typename T>
+__global__ void __launch_bounds__(128) ssm_finish_kernel(const SsmScan P) {
+  const int lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();                // y_raw and the projection are the work of kernels before this one: ld_fresh
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long long)P.n_tokens * P.norm_groups) return;
+  const int t = (int)(item / P.norm_groups), part = (int)(item - (long long)t * P.norm_groups);
+  const int inner = P.n_heads * P.vdim, size = inner / P.norm_groups;
+  const float* y = P.y_raw + (size_t)t * inner + (size_t)part * size;
+  const float* z = P.proj + (size_t)t * P.ld + (size_t)part * size;
+  const float* gain = P.gain + (size_t)part * size;
+  T* out = (T*)P.out + (size_t)t * P.ldo + (size_t)part * size;
+  float ss = 0.f;
+  for (int d = lane; d < size; d += 32) {
+    const float v = ld_fresh(y + d) * ss_silu(ld_fresh(z + d));
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float mul = 1.0f / sqrtf(ss / (float)size + P.eps);
+  for (int d = lane; d < size; d += 32)
+    out[d] = from_float<T>(ld_fresh(y + d) * ss_silu(ld_fresh(z + d)) * mul * gain[d]);
+}
+
+static int ssm_check(const SsmScan& P) {
+  if (P.n_heads < 1 || P.n_groups < 1 || P.n_heads % P.n_groups != 0 || P.vdim < 1 || P.n_state < 1 || P.taps < 1)
+    return STRATUM_ERR_SHAPE;
+  const int inner = P.n_heads * P.vdim, C = inner + 2 * P.n_groups * P.n_state;
+  if (P.norm_groups < 1 || inner % P.norm_groups != 0) return STRATUM_ERR_SHAPE;
+  if (P.ld < inner + C + P.n_heads || P.lda < C + 2 * P.n_heads || P.ldo < inner) return STRATUM_ERR_SHAPE;
+  if ((long long)P.state_stride < (long long)inner * P.n_state + (long long)(P.taps - 1) * C) return STRATUM_ERR_SHAPE;
+  if (P.n_state > 32 * SS_ROWS) return STRATUM_ERR_LIMIT;
+  if (P.n_heads > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
+  return 0;
+}
+
+template <int L>
+static void ssm_recur_launch(const SsmScan& P, cudaStream_t stream) {
+  const int cols = SS_THREADS / L;
+  const dim3 grid((P.vdim + cols - 1) / cols, P.n_heads, P.n_seqs);
+  ssm_recur_kernel<L><<<grid, SS_THREADS, 0, stream>>>(P);
+}
+
+// Everything of a step: prep, recurrence, finish (three launches).  out_dtype: the compute dtype of `out`.
+STRATUM_EXPORT int stratum_ssm_scan(const SsmScan* params, int out_dtype, cudaStream_t stream) {
+  const SsmScan& P = *params;
+  if (P.n_tokens <= 0 || P.n_seqs <= 0) return 0;
+  const int bad = ssm_check(P);
+  if (bad) return bad;
+  launch_pdl(ssm_prep_kernel, P.n_tokens, SS_PREP_THREADS, 0, stream, P);
+  int st = launch_status();
+  if (st) return st;
+  int L = 1;
+  while (SS_ROWS * L < P.n_state) L <<= 1;
+  switch (L) {
+    case 1: ssm_recur_launch<1>(P, stream); break;
+    case 2: ssm_recur_launch<2>(P, stream); break;
+    case 4: ssm_recur_launch<4>(P, stream); break;
+    case 8: ssm_recur_launch<8>(P, stream); break;
+    case 16: ssm_recur_launch<16>(P, stream); break;
+    default: ssm_recur_launch<32>(P, stream); break;
+  }
+  st = launch_status();
+  if (st) return st;
+  const long long items = (long long)P.n_tokens * P.norm_groups;
+  const long long blocks = (items + 3) / 4;
+  if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
+  if (out_dtype == STRATUM_DT_F32) launch_pdl(ssm_finish_kernel<float>, (unsigned)blocks, 128, 0, stream, P);
+  else if (out_dtype == STRATUM_DT_BF16) launch_pdl(ssm_finish_kernel<bf16>, (unsigned)blocks, 128, 0, stream, P);
+  else return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
