@@ -53,13 +53,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 // Activations a matrix product may apply to what it stores (epilogue 0): 0 none,
-// 1 the exact GELU z * 0.5 * (1 + erf(z / sqrt 2)),  2 its tanh form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// 1 the exact GELU z * 0.5 * (1 + erf(z / sqrt 2)),  2 its tanh form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
+// 3 the square of relu, max(z, 0)^2.  The gated epilogue (3: pairs of gate and up) takes the same codes for the
+// gate's activation, with 0 standing for silu there.
 #define STRATUM_ACT_NONE 0
 #define STRATUM_ACT_GELU_ERF 1
 #define STRATUM_ACT_GELU_TANH 2
+#define STRATUM_ACT_RELU_SQ 3
 __device__ __forceinline__ float activate(float z, int act) {
   if (act == STRATUM_ACT_GELU_ERF) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
   if (act == STRATUM_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (act == STRATUM_ACT_RELU_SQ) { const float r = fmaxf(z, 0.f); return r * r; }
   return z;
 }
 

@@ -247,25 +247,26 @@ STRATUM_EXPORT int stratum_gelu(void* x, int dtype, int n_rows, int width, int l
 // a[j] = silu(g[j]) * u[j], silu(z) = z / (1 + exp(-z))   (stratum/native/stratum_engine.h:373-391)
 // gu holds gate and up interleaved: gu[r][2j] = g_j, gu[r][2j+1] = u_j.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int act) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t r = i / inter;
   const int j = (int)(i - r * inter);
   const T* p = gu + r * (size_t)(2 * inter) + 2 * j;
   const float g = to_float(p[0]), u = to_float(p[1]);
-  out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  out[i] = from_float<T>((act ? activate(g, act) : g / (1.0f + expf(-g))) * u);      // act: the gate's, 0 = silu
 }
 
-STRATUM_EXPORT int stratum_swiglu(const void* gu, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
+STRATUM_EXPORT int stratum_swiglu(const void* gu, void* out, int dtype, int n_rows, int inter, int act,
+                                  cudaStream_t stream) {
   const size_t total = (size_t)n_rows * inter;
   if (total == 0) return 0;
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == STRATUM_DT_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total, act);
   else if (dtype == STRATUM_DT_BF16)
-    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total);
+    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total, act);
   else
     return STRATUM_ERR_DTYPE;
   return launch_status();

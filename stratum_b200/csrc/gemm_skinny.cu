@@ -162,7 +162,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       // the unfused path rounds gate and up to bfloat16 before the activation; do the same
       gate = __bfloat162float(__float2bfloat16_rn(gate));
       up = __bfloat162float(__float2bfloat16_rn(up));
-      ((bf16*)out)[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+      ((bf16*)out)[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn((act ? activate(gate, act) : gate / (1.0f + expf(-gate))) * up);
     }
   }
   __syncthreads();          // the partial sums are reused by the next group
@@ -215,7 +215,7 @@ static int launch_skinny(const bf16* x, const bf16* w, const float* bias, void* 
 STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int epilogue,
                                        int M, int N, int K, int ldx, int ldo, int act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (act != 0 && epilogue != 0) return STRATUM_ERR_SHAPE;
+  if (act != 0 && epilogue != 0 && epilogue != 3) return STRATUM_ERR_SHAPE;
   if (M > 32) return STRATUM_ERR_LIMIT;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return STRATUM_ERR_SHAPE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return STRATUM_ERR_ALIGN;

@@ -182,7 +182,7 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col
       for (int e = 0; e < 2; e++) {
         const float gate = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e]));
         const float up = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e + 1]));
-        a[e] = gate / (1.0f + __expf(-gate)) * up;
+        a[e] = (P.X.act ? activate(gate, P.X.act) : gate / (1.0f + __expf(-gate))) * up;
       }
       __nv_bfloat162 pr = __floats2bfloat162_rn(a[0], a[1]);
       packed[j / 4] = *reinterpret_cast<uint32_t*>(&pr);
@@ -284,7 +284,7 @@ __device__ __forceinline__ void fixup_store(const PT& P, int m, int n, float4 v)
     for (int j = 0; j < 4; j += 2) {
       if (n + j + 1 < P.N) {
         const float g = __bfloat162float(__float2bfloat16_rn(e[j])), u = __bfloat162float(__float2bfloat16_rn(e[j + 1]));
-        o[j >> 1] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+        o[j >> 1] = __float2bfloat16_rn((P.X.act ? activate(g, P.X.act) : g / (1.0f + __expf(-g))) * u);
       }
     }
     return;
@@ -827,7 +827,7 @@ __device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, i
       val = __bfloat162float(__float2bfloat16_rn(val));
       const float other = __shfl_xor_sync(0xffffffffu, val, 1);     // gate (even n) <-> up (odd n)
       if (m < P.M && n + 1 < P.N && (n & 1) == 0)
-        ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn(val / (1.0f + __expf(-val)) * other);
+        ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn((P.X.act ? activate(val, P.X.act) : val / (1.0f + __expf(-val))) * other);
     } else if (m < P.M && n < P.N) {
       const size_t idx = (size_t)m * P.ldo + n;
       if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(activate(val, P.X.act));

@@ -10,7 +10,11 @@
 //                  the key cache [pages][n_k][page_tokens][k_dim];
 //                  with k_out the same numbers also go to row t of that matrix (rows of tokens of no sequence: zeros);
 //   value head j   goes to the value cache [pages][n_v][page_tokens][v_dim]  (n_v = 0: the mixer keeps no values).
-// Rotation: pair (i, i + R), i < R, angle a = (float)p * inv_freq[i]:  (u, v) -> (u cos a - v sin a, v cos a + u sin a).
+// Rotation: pair (i, i + R), i < R (or, with `interleaved`, the neighbours (2i, 2i + 1)), angle a = (float)p *
+// inv_freq[i]:  (u, v) -> (u cos a - v sin a, v cos a + u sin a).
+//
+// gate_heads: a[t][j * block + i] *= sigmoid(g[t][j]): every head's stretch of a row times the head's gate, whose
+// pre-activation is a column of a projection.
 // Everything is evaluated in float32 and rounded once to the storage type.  One block per token; the order of
 // every sum depends on the row alone.
 #include <math.h>
@@ -35,7 +39,7 @@ struct MixerPrep {
   int page_tokens, write_cache;
   float eps;
   int q_out_ld, q_out_step, q_out_off;
-  int k_out_ld, reserved;
+  int k_out_ld, interleaved;
 };
 
 template <typename T>
@@ -74,10 +78,11 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(const MixerPrep P) {
     T* u = x + P.q_col + (size_t)j * P.q_dim + P.q_rot_off;
     T* w = qo ? qo + (size_t)j * P.q_out_step : u;
     if (i < R) {
-      const float a = ld_fresh(u + i), b = ld_fresh(u + i + R);
+      const int ia = P.interleaved ? 2 * i : i, ib = P.interleaved ? 2 * i + 1 : i + R;
+      const float a = ld_fresh(u + ia), b = ld_fresh(u + ib);
       const float2 f = mp_cs[i];
-      w[i] = from_float<T>(a * f.x - b * f.y);
-      w[i + R] = from_float<T>(b * f.x + a * f.y);
+      w[ia] = from_float<T>(a * f.x - b * f.y);
+      w[ib] = from_float<T>(b * f.x + a * f.y);
     } else {
       w[i + R] = from_float<T>(ld_fresh(u + i + R));
     }
@@ -102,7 +107,11 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(const MixerPrep P) {
         v = v * mul * P.k_norm_gain[d];
       } else if (d >= P.k_rot_off && d < P.k_rot_off + 2 * R) {
         const int i = d - P.k_rot_off;
-        if (i < R) {
+        if (P.interleaved) {
+          const float2 f = mp_cs[i >> 1];
+          const float other = ld_fresh(k + d + ((i & 1) ? -1 : 1));
+          v = (i & 1) ? v * f.x + other * f.y : v * f.x - other * f.y;
+        } else if (i < R) {
           const float2 f = mp_cs[i];
           v = v * f.x - ld_fresh(k + d + R) * f.y;
         } else {
@@ -119,6 +128,37 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(const MixerPrep P) {
     T* dst = (T*)P.v_cache + ((row * P.n_v + j) * P.page_tokens + in_page) * (size_t)P.v_dim;
     dst[d] = from_float<T>(ld_fresh(x + P.v_col + it));
   }
+}
+
+template <typename T>
+__global__ void gate_heads_kernel(T* a, int lda, const T* g, int ldg, int n_heads, int block, size_t total) {
+  pdl_trigger();
+  pdl_wait();                                        // a and g are the work of kernels before this one: ld_fresh
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int width = n_heads * block;
+  const size_t t = i / width;
+  const int c = (int)(i - t * width);
+  const float z = ld_fresh((const T*)g + t * ldg + c / block);
+  T* p = a + t * lda + c;
+  *p = from_float<T>(ld_fresh((const T*)p) / (1.0f + expf(-z)));
+}
+
+STRATUM_EXPORT int stratum_gate_heads(void* a, int lda, const void* g, int ldg, int n_rows, int n_heads, int block,
+                                      int dtype, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * n_heads * block;
+  if (total == 0) return 0;
+  if (n_heads < 1 || block < 1 || lda < n_heads * block || ldg < n_heads) return STRATUM_ERR_SHAPE;
+  const size_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffULL) return STRATUM_ERR_LIMIT;
+  if (dtype == STRATUM_DT_F32)
+    launch_pdl(gate_heads_kernel<float>, (unsigned)blocks, 256, 0, stream, (float*)a, lda, (const float*)g, ldg,
+               n_heads, block, total);
+  else if (dtype == STRATUM_DT_BF16)
+    launch_pdl(gate_heads_kernel<bf16>, (unsigned)blocks, 256, 0, stream, (bf16*)a, lda, (const bf16*)g, ldg, n_heads,
+               block, total);
+  else return STRATUM_ERR_DTYPE;
+  return launch_status();
 }
 
 STRATUM_EXPORT int stratum_mixer_prep(const MixerPrep* params, int dtype, cudaStream_t stream) {

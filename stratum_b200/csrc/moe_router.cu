@@ -7,6 +7,10 @@
 //   their weights are s_e / (sum of the chosen s + 1e-20) * scale.  Written: the chosen experts and their weights
 //   [tokens][top], and the same as a row of n_experts weights with zeros for the others.
 //   One block per token; a sum's order depends on the row's length alone.
+//   Variants, all parameters: score = 1 takes s = softmax(z) over all experts in sigmoid's place; renorm = 0 leaves
+//   the chosen scores as they are (weight s_e * scale); correction may be absent; with w_gate (one more row of
+//   `width` weights) the token's sigmoid(w_gate . h) is written behind the experts' weights, dense[t][n_experts]:
+//   the gate of a shared expert.
 // scale_column_blocks: a[t][e * block + j] *= w[t][e] for e < n_blocks (columns beyond n_blocks * block are left
 //   alone): the activations of every expert, side by side in one row, times the token's weight for that expert, so
 //   that one product with the experts' stacked down matrices sums the weighted expert outputs.
@@ -28,6 +32,8 @@ struct MoeRoute {
   int ldx, ldd, n_tokens, width;
   int n_experts, top, n_groups, keep;
   float scale, reserved;
+  const float* w_gate;      // [width] or null
+  int score, renorm;        // score: 0 sigmoid, 1 softmax over all experts;  renorm: weights divided by their sum
 };
 
 #define MR_WARPS 8
@@ -46,9 +52,11 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
   float* c = s + E;
   float* gs = c + E;
   const T* x = (const T*)P.x + (size_t)t * P.ldx;
-  const bool vec = P.width % 4 == 0 && (((uintptr_t)x | (uintptr_t)P.w_router) & 15) == 0 && (P.ldx * sizeof(T)) % 16 == 0;
-  for (int e = warp; e < E; e += MR_WARPS) {
-    const float* w = P.w_router + (size_t)e * P.width;
+  const bool vec = P.width % 4 == 0 && (((uintptr_t)x | (uintptr_t)P.w_router | (uintptr_t)P.w_gate) & 15) == 0 &&
+                   (P.ldx * sizeof(T)) % 16 == 0;
+  const int n_rows = E + (P.w_gate ? 1 : 0);         // the gate of a shared expert is one more row
+  for (int e = warp; e < n_rows; e += MR_WARPS) {
+    const float* w = e < E ? P.w_router + (size_t)e * P.width : P.w_gate;
     float acc = 0.f;
     if (vec) {
       // four stretches of four elements in flight per lane, each with a sum of its own; the sums are added in one
@@ -91,12 +99,36 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
     acc = warp_sum(acc);
     if (lane == 0) {
       const float sg = 1.0f / (1.0f + expf(-acc));
-      s[e] = sg;
-      c[e] = sg + P.correction[e];
+      if (e == E) {
+        P.dense[(size_t)t * P.ldd + E] = sg;
+      } else if (P.score == 1) {
+        s[e] = acc;                                  // the logit; the softmax follows once all are there
+      } else {
+        s[e] = sg;
+        c[e] = sg + (P.correction ? P.correction[e] : 0.f);
+      }
     }
   }
   __syncthreads();
   if (warp != 0) return;
+  if (P.score == 1) {
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, s[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(s[e] - m);
+      s[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      const float v = s[e] / sum;
+      s[e] = v;
+      c[e] = v + (P.correction ? P.correction[e] : 0.f);
+    }
+    __syncwarp();
+  }
   // group scores, then all but the `keep` best groups are closed
   for (int g = lane; g < G; g += 32) {
     float a = -INFINITY, b = -INFINITY;              // the two largest
@@ -139,7 +171,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
     }
     __syncwarp();
   }
-  const float mul = P.scale / (total + 1e-20f);
+  const float mul = P.renorm ? P.scale / (total + 1e-20f) : P.scale;
   for (int k = lane; k < P.top; k += 32) {
     const int e = P.chosen[(size_t)t * P.top + k];
     const float w = s[e] * mul;
@@ -152,7 +184,8 @@ STRATUM_EXPORT int stratum_moe_route(const MoeRoute* params, int dtype, cudaStre
   const MoeRoute& P = *params;
   if (P.n_tokens <= 0) return 0;
   if (P.n_experts < 1 || P.n_groups < 1 || P.n_experts % P.n_groups != 0 || P.keep < 1 || P.keep > P.n_groups ||
-      P.top < 1 || P.top > (P.n_experts / P.n_groups) * P.keep || P.ldd < P.n_experts || P.ldx < P.width)
+      P.top < 1 || P.top > (P.n_experts / P.n_groups) * P.keep || P.ldd < P.n_experts + (P.w_gate ? 1 : 0) ||
+      P.ldx < P.width)
     return STRATUM_ERR_SHAPE;
   const size_t smem = (size_t)(2 * P.n_experts + P.n_groups) * sizeof(float);
   if (smem > 48 * 1024) return STRATUM_ERR_LIMIT;

@@ -66,16 +66,21 @@ def takes_tensor_cores(x: torch.Tensor, w: torch.Tensor, extras: bool) -> bool:
 
 def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
         extra=None, act: int = 0) -> None:
-    """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py.  act (STORE only): an activation
-    applied to what is stored (kernels.ACT_*), by whichever kernel takes the call."""
+    """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py.  act: with STORE an activation
+    applied to what is stored, with SWIGLU the gate's activation in silu's place (kernels.ACT_*), by whichever
+    kernel takes the call."""
     if act:
-        if mode != STORE or extra is not None:
-            raise K.KernelError("an activation goes with the plain store epilogue")
+        if mode not in (STORE, SWIGLU) or extra is not None:
+            raise K.KernelError("an activation goes with the plain store epilogue or the gated one")
         if x.dtype == torch.bfloat16 and _aligned(x, w):
             if x.shape[0] <= SKINNY_MAX_ROWS and w.numel() < STREAMK_MIN_WEIGHTS:
                 K.gemm_skinny(x, w, bias, out, mode, act)
             else:
                 K.gemm_tc(x, w, bias, out, mode, K.GemmExtra().activation(act))
+        elif mode == SWIGLU:
+            gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+            K.linear_simple(x, w, bias, gu, STORE)
+            K.swiglu(gu, out, act)
         else:
             K.linear_simple(x, w, bias, out, mode, act)
         return

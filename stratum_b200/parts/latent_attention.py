@@ -19,6 +19,12 @@ the bfloat16 path, where attention over a long prompt is bound by the tensor cor
 [Wuk_j c | kr] come from one product of the step's rows [c | kr] with the matrix that stacks [Wuk_j 0; 0 I] per
 head, the values from Wuv c, and the general attention reads them as plain matrices.  The cache is written all
 the same, for the steps that follow.
+
+Two optional pieces, each a parameter.  Queries through a latent of their own (`q_rank`): cq = Wdq h / rms * gq,
+q = Wuq cq; the down projection joins the fused first product, the norm runs in place on its stretch of the row
+(float32 statistic), and the up projection writes the queries where the direct projection would have.  A gate per
+head (`gate`): head j's output times sigmoid(Wg h)_j, whose pre-activation is one more column stretch of the first
+product; the sigmoid is taken in float32 on the heads' outputs, in front of the output projection.
 """
 from __future__ import annotations
 
@@ -32,7 +38,7 @@ from .. import kernels as K
 from ..cache.pages import PAGE_TOKENS
 from ..cache.store import KVSpec, LayerCache
 from .base import Mixer
-from .linear import ADD_TO_F32, STORE, HeadLinear, Linear
+from .linear import ADD_TO_F32, STORE, STORE_F32, HeadLinear, Linear
 from .registry import find_part, register_part
 from .spec import PartSpec, TensorSpec
 
@@ -49,9 +55,12 @@ def padded(n: int, to: int = 8) -> int:
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
     """params: hidden, n_heads, head_dim (the unrotated query/key size), rot_dim, v_dim, kv_rank, scale, eps (of
-    the latent's norm), position (PartSpec of a rotating position encoding over at most rot_dim dimensions),
-    window (0 = all keys), prefix, and the tensor names q, dkv, dkv_norm, uk, uv, o (defaults: those words, with
-    "dkv.norm")."""
+    the latents' norms), position (PartSpec of a rotating position encoding over at most rot_dim dimensions, pairs
+    (i, i + n/2) or neighbours (2i, 2i + 1) as the encoding says), window (0 = all keys), q_rank (None or 0: queries
+    projected directly from the input; else the size of the queries' latent), gate (a sigmoid gate per head on the
+    heads' outputs), prefix, and the tensor names q, dkv, dkv_norm, uk, uv, o, and with q_rank dq, dq_norm, uq, with
+    gate g (defaults: those words, with "dkv.norm" and "dq.norm")."""
+    stores_output = True
 
     @property
     def replays_prompts(self) -> bool:
@@ -67,13 +76,25 @@ class LatentAttention(Mixer):
         pos: PartSpec = spec["position"]
         self.position = find_part("position", pos.kind)(pos, runtime)
         layout = self.position.pair_layout()
-        if layout is None or layout[1] or 2 * layout[0] > self.r:
-            raise ValueError("latent attention rotates pairs (i, i + n/2) of at most rot_dim dimensions")
-        self.names = {k: self.prefix + str(spec.get(k, k if k != "dkv_norm" else "dkv.norm"))
-                      for k in ("q", "dkv", "dkv_norm", "uk", "uv", "o")}
+        if layout is None or 2 * layout[0] > self.r:
+            raise ValueError("latent attention rotates pairs of at most rot_dim dimensions")
+        self.interleaved = bool(layout[1])
+        self.q_rank = int(spec.get("q_rank") or 0)
+        self.gate = bool(spec.get("gate", False))
+        self.names = {k: self.prefix + str(spec.get(k, k.replace("_norm", ".norm")))
+                      for k in ("q", "dkv", "dkv_norm", "uk", "uv", "o", "dq", "dq_norm", "uq", "g")}
+        # columns of a token's row of projections: [queries | c' kr | the queries' latent | the gates], every
+        # stretch starting at a multiple of 8 (16 bytes in bfloat16: rows a product may read or write by vectors)
+        self.q_cols = self.n_heads * (self.d + self.r)
+        self.kv_col = padded(self.q_cols) if self.q_rank else self.q_cols
+        self.cq_col = self.kv_col + padded(self.rank + self.r)
+        self.g_col = self.cq_col + padded(self.q_rank)
+        self.width = (self.g_col + self.n_heads if self.gate else
+                      self.cq_col + self.q_rank if self.q_rank else self.kv_col + self.rank + self.r)
         self.shape = K.AttentionShape(self.n_heads, self.n_heads, 1, self.rank + self.r, self.rank, True, self.scale,
                                       window=self.window)
         self.w_in: Optional[Linear] = None
+        self.w_uq: Optional[Linear] = None
         self.w_o: Optional[Linear] = None
         self.uk: Optional[HeadLinear] = None
         self.uv: Optional[HeadLinear] = None
@@ -81,16 +102,44 @@ class LatentAttention(Mixer):
 
     def tensors(self) -> Dict[str, TensorSpec]:
         n, H = self.names, self.n_heads
-        return {n["q"]: TensorSpec((H * (self.d + self.r), self.hidden)),
-                n["dkv"]: TensorSpec((self.rank + self.r, self.hidden)),
-                n["dkv_norm"]: TensorSpec((self.rank,), role="vector", init="ones"),
-                n["uk"]: TensorSpec((H * self.d, self.rank)),
-                n["uv"]: TensorSpec((H * self.dv, self.rank)),
-                n["o"]: TensorSpec((self.hidden, H * self.dv))}
+        t = {n["dkv"]: TensorSpec((self.rank + self.r, self.hidden)),
+             n["dkv_norm"]: TensorSpec((self.rank,), role="vector", init="ones"),
+             n["uk"]: TensorSpec((H * self.d, self.rank)),
+             n["uv"]: TensorSpec((H * self.dv, self.rank)),
+             n["o"]: TensorSpec((self.hidden, H * self.dv))}
+        if self.q_rank:
+            t.update({n["dq"]: TensorSpec((self.q_rank, self.hidden)),
+                      n["dq_norm"]: TensorSpec((self.q_rank,), role="vector", init="ones"),
+                      n["uq"]: TensorSpec((self.q_cols, self.q_rank))})
+        else:
+            t[n["q"]] = TensorSpec((self.q_cols, self.hidden))
+        if self.gate:
+            t[n["g"]] = TensorSpec((H, self.hidden))
+        return t
+
+    def _stack_rows(self, pieces) -> torch.Tensor:
+        """The matrices of `pieces` ((first row, matrix) pairs) one above the other, each from its row on, zero rows
+        between them: the weight of one product whose output stretches start where the row layout says."""
+        first = min(at for at, _ in pieces)
+        last = max(at + w.shape[0] for at, w in pieces)
+        ref = pieces[0][1]
+        out = torch.zeros((last - first, self.hidden), dtype=ref.dtype, device=ref.device)
+        for at, w in pieces:
+            out[at - first:at - first + w.shape[0]] = w
+        return out
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         n, H = self.names, self.n_heads
-        self.w_in = Linear(self.runtime, torch.cat([weights[n["q"]], weights[n["dkv"]]], dim=0).contiguous())
+        pieces = [(self.kv_col, weights[n["dkv"]])]
+        if self.q_rank:
+            pieces.append((self.cq_col, weights[n["dq"]]))
+            self.w_uq = Linear(self.runtime, weights[n["uq"]])
+            self.gain_q = weights[n["dq_norm"]].contiguous()
+        else:
+            pieces.append((0, weights[n["q"]]))
+        if self.gate:
+            pieces.append((self.g_col, weights[n["g"]]))
+        self.w_in = Linear(self.runtime, self._stack_rows(pieces))
         self.gain = weights[n["dkv_norm"]]
         # head j carries its plain query into the latent space with Wuk_j^T: a matrix [rank, d] per head
         self.uk = HeadLinear(self.runtime, weights[n["uk"]].view(H, self.d, self.rank).transpose(1, 2).contiguous())
@@ -121,14 +170,21 @@ class LatentAttention(Mixer):
         before = (step.host or {}).get("before")
         return bool(before) and all(b == 0 for b in before) and step.max_new >= PER_HEAD_MIN_TOKENS
 
-    def _forward_per_head(self, proj, step, cache: LayerCache, residual: torch.Tensor) -> None:
+    def _finish(self, heads: torch.Tensor, proj: torch.Tensor, residual: torch.Tensor, store: bool) -> None:
+        """The heads' outputs times their gates (where the mixer has them), then the output projection."""
+        H, dv = self.n_heads, self.dv
+        if self.gate:
+            K.gate_heads(heads, proj[:, self.g_col:self.g_col + H], H, dv)
+        self.w_o(heads[:, :H * dv], out=residual, mode=STORE_F32 if store else ADD_TO_F32)
+
+    def _forward_per_head(self, proj, step, cache: LayerCache, residual: torch.Tensor, store: bool) -> None:
         H, d, r, rank, dv = self.n_heads, self.d, self.r, self.rank, self.dv
         T = proj.shape[0]
-        q_cols = H * (d + r)
         rows = self.runtime.empty(T, padded(rank + r))            # [c | kr] of the step's tokens
         K.mixer_prep(proj, step.token_pos, step.token_seq, cache.block_table, cache.k, None, PAGE_TOKENS, True,
-                     queries=(H, d + r, 0), q_rot_off=d, keys=(1, rank + r, q_cols), k_rot_off=rank,
-                     inv_freq=self.position.rotary().inv_freq, k_norm_gain=self.gain, eps=self.eps, k_out=rows)
+                     queries=(H, d + r, 0), q_rot_off=d, keys=(1, rank + r, self.kv_col), k_rot_off=rank,
+                     inv_freq=self.position.rotary().inv_freq, k_norm_gain=self.gain, eps=self.eps, k_out=rows,
+                     interleaved=self.interleaved)
         # 64 rows beyond the step's: the last tile of the last sequence reads (and ignores) them
         keys = self.runtime.empty(T + PAGE_TOKENS, padded(H * (d + r)))
         values = self.runtime.empty(T + PAGE_TOKENS, padded(H * dv))
@@ -139,26 +195,32 @@ class LatentAttention(Mixer):
         heads = self.runtime.empty(T, padded(H * dv))
         from . import attention_dispatch
         attention_dispatch.run_general_dense(self, self.head_shape, proj, keys, values, step, heads)
-        self.w_o(heads[:, :H * dv], out=residual, mode=ADD_TO_F32)
+        self._finish(heads, proj, residual, store)
 
-    def forward(self, xn, residual: torch.Tensor, step, cache: LayerCache, emit=None) -> None:
+    def forward(self, xn, residual: torch.Tensor, step, cache: LayerCache, emit=None, store: bool = False) -> None:
         H, d, r, rank, dv = self.n_heads, self.d, self.r, self.rank, self.dv
         T = xn.shape[0]
-        q_cols, width = H * (d + r), H * (d + r) + rank + r
-        proj = self.runtime.empty(T, padded(width))
-        self.w_in(xn, out=proj[:, :width], mode=STORE)
+        proj = self.runtime.empty(T, padded(self.width))
+        if self.q_rank:
+            # [c' kr | cq' | gates] in one product; the queries' latent is normed in place and expanded into the
+            # queries' columns
+            self.w_in(xn, out=proj[:, self.kv_col:self.width], mode=STORE)
+            K.rmsnorm_heads(proj, self.cq_col, 1, self.q_rank, self.gain_q, self.eps)
+            self.w_uq(proj[:, self.cq_col:self.cq_col + self.q_rank], out=proj[:, :self.q_cols], mode=STORE)
+        else:
+            self.w_in(xn, out=proj[:, :self.width], mode=STORE)
         if self._per_head_form(step, cache) and K.attention_general_mma_ok(self.head_shape, proj, proj, PAGE_TOKENS):
-            self._forward_per_head(proj, step, cache, residual)
+            self._forward_per_head(proj, step, cache, residual, store)
             return
         q_lat = self.runtime.empty(T, padded(H * (rank + r)))
         K.mixer_prep(proj, step.token_pos, step.token_seq, cache.block_table, cache.k, None, PAGE_TOKENS, cache.writes,
-                     queries=(H, d + r, 0), q_rot_off=d, keys=(1, rank + r, q_cols), k_rot_off=rank,
+                     queries=(H, d + r, 0), q_rot_off=d, keys=(1, rank + r, self.kv_col), k_rot_off=rank,
                      inv_freq=self.position.rotary().inv_freq, k_norm_gain=self.gain, eps=self.eps,
-                     q_out=q_lat, q_out_step=rank + r, q_out_off=rank)
+                     q_out=q_lat, q_out_step=rank + r, q_out_off=rank, interleaved=self.interleaved)
         self.uk(proj, d + r, q_lat, rank + r)
         mixed = self.runtime.empty(T, padded(H * rank))
         from . import attention_dispatch
         attention_dispatch.run_general(self, self.shape, q_lat, cache, step, mixed)
         heads = self.runtime.empty(T, padded(H * dv))
         self.uv(mixed, rank, heads, dv)
-        self.w_o(heads[:, :H * dv], out=residual, mode=ADD_TO_F32)
+        self._finish(heads, proj, residual, store)

@@ -33,8 +33,8 @@ class Linear:
         SWIGLU: rows of W alternate gate and up, out[m][j] = silu(y[m][2j]) * y[m][2j+1] in x's dtype;
         QKV_ROPE: see kernels.GemmExtra (extra carries the cache and the rotation table; out: the query rows).
         x may be NormedRows (the product then applies the norm's row factors).  emit: a Handover that the
-        ADD_TO_F32 product honours where it can (emit.result is then set).  act (STORE only): an activation the
-        product applies to what it stores (kernels.ACT_*)."""
+        ADD_TO_F32 product honours where it can (emit.result is then set).  act: with STORE an activation the
+        product applies to what it stores, with SWIGLU the gate's activation in silu's place (kernels.ACT_*)."""
         from . import gemm_dispatch
         from .base import NormedRows
         normed = x if isinstance(x, NormedRows) else None

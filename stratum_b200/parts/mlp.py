@@ -15,7 +15,7 @@ import torch
 
 from .base import FeedForward
 from .. import kernels as K
-from .linear import ADD_TO_F32, STORE, SWIGLU, Linear
+from .linear import ADD_TO_F32, STORE, STORE_F32, SWIGLU, Linear
 from .registry import register_part
 from .spec import TensorSpec
 
@@ -25,41 +25,56 @@ def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return torch.stack([a, b], dim=1).reshape((a.shape[0] * 2,) + tuple(a.shape[1:])).contiguous()
 
 
+GATE_ACTS = {"silu": K.ACT_NONE, "gelu_erf": K.ACT_GELU_ERF, "gelu_tanh": K.ACT_GELU_TANH, "relu_sq": K.ACT_RELU_SQ}
+
+
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden, intermediate, bias, prefix."""
+    """A gated feed-forward: Wd (act(Wg xn) * (Wu xn)), act = silu unless `activation` names another ("gelu_tanh",
+    "gelu_erf", "relu_sq").  params: hidden, intermediate, bias, prefix, activation, and the tensors' names gate, up,
+    down (defaults "gate_proj.weight" ... with biases "gate_proj.bias" ...; a name given in full has its bias at
+    name + ".b")."""
     replays_prompts = True
     takes_normed_rows = True
     hands_on = True
+    stores_output = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden"])
         self.intermediate = int(spec["intermediate"])
         self.bias = bool(spec.get("bias", False))
+        act = spec.get("activation", "silu")
+        if act not in GATE_ACTS:
+            raise ValueError(f"gated feed-forward: activation {act!r} is not one of {sorted(GATE_ACTS)}")
+        self.act = GATE_ACTS[act]
+        self.w_names, self.b_names = {}, {}
+        for key in ("gate", "up", "down"):
+            given = spec.get(key)
+            self.w_names[key] = self.prefix + (given if given else f"{key}_proj.weight")
+            self.b_names[key] = self.prefix + (given + ".b" if given else f"{key}_proj.bias")
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        p, H, F = self.prefix, self.hidden, self.intermediate
-        t = {p + "gate_proj.weight": TensorSpec((F, H)), p + "up_proj.weight": TensorSpec((F, H)),
-             p + "down_proj.weight": TensorSpec((H, F))}
+        H, F = self.hidden, self.intermediate
+        w, b = self.w_names, self.b_names
+        t = {w["gate"]: TensorSpec((F, H)), w["up"]: TensorSpec((F, H)), w["down"]: TensorSpec((H, F))}
         if self.bias:
-            t.update({p + "gate_proj.bias": TensorSpec((F,), role="vector"),
-                      p + "up_proj.bias": TensorSpec((F,), role="vector"),
-                      p + "down_proj.bias": TensorSpec((H,), role="vector")})
+            t.update({b["gate"]: TensorSpec((F,), role="vector"), b["up"]: TensorSpec((F,), role="vector"),
+                      b["down"]: TensorSpec((H,), role="vector")})
         return t
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
-        p = self.prefix
-        w = interleave_rows(weights[p + "gate_proj.weight"], weights[p + "up_proj.weight"])
-        b = interleave_rows(weights[p + "gate_proj.bias"], weights[p + "up_proj.bias"]) if self.bias else None
+        wn, bn = self.w_names, self.b_names
+        w = interleave_rows(weights[wn["gate"]], weights[wn["up"]])
+        b = interleave_rows(weights[bn["gate"]], weights[bn["up"]]) if self.bias else None
         self.gate_up = Linear(self.runtime, w, b)
-        self.down = Linear(self.runtime, weights[p + "down_proj.weight"], weights.get(p + "down_proj.bias"))
+        self.down = Linear(self.runtime, weights[wn["down"]], weights.get(bn["down"]) if self.bias else None)
 
-    def forward(self, xn, residual: torch.Tensor, step, emit=None) -> None:
-        a = self.gate_up(xn, mode=SWIGLU)
-        self.down(a, out=residual, mode=ADD_TO_F32, emit=emit)
+    def forward(self, xn, residual: torch.Tensor, step, emit=None, store: bool = False) -> None:
+        a = self.gate_up(xn, mode=SWIGLU, act=self.act)
+        self.down(a, out=residual, mode=STORE_F32 if store else ADD_TO_F32, emit=None if store else emit)
 
 
 @register_part("feed_forward", "dense_gelu")

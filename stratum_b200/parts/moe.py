@@ -22,6 +22,12 @@ Two ways to run the experts, chosen by the step's size:
 
 Either way an expert a token did not choose contributes nothing, and a token's sum has a fixed order, so the result
 does not depend on the other tokens of the step beyond the rounding of the products.
+
+Variants, each a parameter: scores by softmax over all experts in sigmoid's place (`score`); the chosen scores used as
+they are, not divided by their sum (`renorm` false); no correction tensor (`correction` false); experts without a gate
+matrix, Wdown act(Wup h), with the activation named (`gated` false, `activation`); and a shared expert whose output is
+multiplied by sigmoid(w_sg . h), one number per token (`shared_gate`: the name of that row of weights): the router's
+kernel takes that dot product with the experts' and leaves the gate beside the experts' weights.
 """
 from __future__ import annotations
 
@@ -33,8 +39,8 @@ import torch
 
 from .. import kernels as K
 from .base import FeedForward
-from .linear import ADD_TO_F32, STORE_F32, SWIGLU, Linear
-from .mlp import interleave_rows
+from .linear import ADD_TO_F32, STORE, STORE_F32, SWIGLU, Linear
+from .mlp import GATE_ACTS, interleave_rows
 from .registry import register_part
 from .spec import TensorSpec
 
@@ -48,8 +54,9 @@ GROUPED_MIN_ROWS = int(os.environ.get("STRATUM_MOE_GROUPED_MIN_ROWS", 96))
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
     """params: hidden, n_experts, top, scale, n_groups, keep, intermediate (of an expert), shared_intermediate (of
-    the shared expert; None: none), prefix.  Tensors: router, correction, e<i>.gate / .up / .down,
-    shared.gate / .up / .down."""
+    the shared expert; None: none), prefix; score ("sigmoid" or "softmax"), renorm, correction, gated, activation
+    ("silu", "gelu_tanh", "gelu_erf", "relu_sq"), shared_gate (tensor name under the prefix, or None).  Tensors:
+    router, correction, e<i>.gate / .up / .down, shared.gate / .up / .down (no .gate when not gated)."""
     stores_output = True
 
     def __init__(self, spec, runtime):
@@ -63,6 +70,20 @@ class RoutedExperts(FeedForward):
         if self.n_experts % self.n_groups or self.keep > self.n_groups \
                 or self.top > (self.n_experts // self.n_groups) * self.keep:
             raise ValueError("routed_experts: experts, groups, keep and top do not fit together")
+        score = spec.get("score", "sigmoid")
+        if score not in ("sigmoid", "softmax"):
+            raise ValueError(f"routed_experts: score {score!r} is neither 'sigmoid' nor 'softmax'")
+        self.softmax = score == "softmax"
+        self.renorm = bool(spec.get("renorm", True))
+        self.has_correction = bool(spec.get("correction", True))
+        self.gated = bool(spec.get("gated", True))
+        act = spec.get("activation", "silu")
+        if act not in GATE_ACTS or (not self.gated and act == "silu"):
+            raise ValueError(f"routed_experts: activation {act!r} is not known"
+                             + ("" if self.gated else " to experts without a gate"))
+        self.act = GATE_ACTS[act]
+        self.shared_gate = spec.get("shared_gate") if self.shared_ff else None
+        self.correction = self.w_gate = None
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -71,39 +92,55 @@ class RoutedExperts(FeedForward):
 
     def tensors(self) -> Dict[str, TensorSpec]:
         p, H = self.prefix, self.hidden
-        t = {p + "router": TensorSpec((self.n_experts, H), role="vector"),
-             p + "correction": TensorSpec((self.n_experts,), role="vector", init="zeros")}
+        t = {p + "router": TensorSpec((self.n_experts, H), role="vector")}
+        if self.has_correction:
+            t[p + "correction"] = TensorSpec((self.n_experts,), role="vector", init="zeros")
+        if self.shared_gate:
+            t[p + self.shared_gate] = TensorSpec((1, H), role="vector")
         for e in self._experts():
             ff = self.shared_ff if e == "shared." else self.ff
-            t.update({p + e + "gate": TensorSpec((ff, H)), p + e + "up": TensorSpec((ff, H)),
-                      p + e + "down": TensorSpec((H, ff))})
+            t.update({p + e + "up": TensorSpec((ff, H)), p + e + "down": TensorSpec((H, ff))})
+            if self.gated:
+                t[p + e + "gate"] = TensorSpec((ff, H))
         return t
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.router, self.correction = weights[p + "router"].contiguous(), weights[p + "correction"].contiguous()
+        self.router = weights[p + "router"].contiguous()
+        if self.has_correction:
+            self.correction = weights[p + "correction"].contiguous()
+        if self.shared_gate:
+            self.w_gate = weights[p + self.shared_gate].reshape(-1).contiguous()
         names = self._experts()
-        gates = torch.cat([weights[p + e + "gate"] for e in names], dim=0)
         ups = torch.cat([weights[p + e + "up"] for e in names], dim=0)
-        stacked = interleave_rows(gates, ups)
+        # rows of an expert in the stacked first matrix: gate and up alternating, or the up matrix alone
+        per = 2 if self.gated else 1
+        stacked = interleave_rows(torch.cat([weights[p + e + "gate"] for e in names], dim=0), ups) if self.gated \
+            else ups.contiguous()
         self.gate_up = Linear(self.runtime, stacked)
         self.down = Linear(self.runtime, torch.cat([weights[p + e + "down"] for e in names], dim=1).contiguous())
         # the grouped way: every expert's matrices by themselves (gate|up: stretches of the stacked rows; down: the
         # tensors as loaded, since a stretch of the stacked matrix's columns is not a matrix a product can take)
-        first = [2 * self.ff * i for i in range(self.n_experts)] + [2 * self.ff * self.n_experts]
-        sizes = [2 * self.ff] * self.n_experts + [2 * self.shared_ff]
+        first = [per * self.ff * i for i in range(self.n_experts)] + [per * self.ff * self.n_experts]
+        sizes = [per * self.ff] * self.n_experts + [per * self.shared_ff]
         self.gate_up_of = [Linear(self.runtime, stacked[a:a + n]) for a, n in zip(first, sizes) if n]
         self.down_of = [Linear(self.runtime, weights[p + e + "down"].contiguous()) for e in names]
 
     def route(self, xin: torch.Tensor):
         """(dense weights [T, experts] with zeros for experts not chosen, chosen [T, top], their weights [T, top])."""
         T = xin.shape[0]
-        dense = self.runtime.empty(T, self.n_experts, dtype=torch.float32)
+        dense = self.runtime.empty(T, self.n_experts + (1 if self.w_gate is not None else 0), dtype=torch.float32)
         chosen = self.runtime.empty(T, self.top, dtype=torch.int32)
         weights = self.runtime.empty(T, self.top, dtype=torch.float32)
         K.moe_route(xin, self.router, self.correction, dense, chosen, weights, self.top, self.n_groups, self.keep,
-                    self.scale)
+                    self.scale, softmax=self.softmax, renorm=self.renorm, w_gate=self.w_gate)
         return dense, chosen, weights
+
+    def _first(self, lin: Linear, x: torch.Tensor) -> torch.Tensor:
+        """An expert's (or all experts') activations: act(gate) * up, or act(up) where the experts have no gate."""
+        if self.gated:
+            return lin(x, mode=SWIGLU, act=self.act)
+        return lin(x, mode=STORE, act=self.act)
 
     def grouped(self, step, n_tokens: int) -> bool:
         """Whether this step takes the grouped way: a prompt step (never a step that may be captured and replayed: the
@@ -127,9 +164,12 @@ class RoutedExperts(FeedForward):
     def forward(self, xin, residual: torch.Tensor, step, store: bool = False) -> None:
         dense, chosen, weights = self.route(xin)
         T = xin.shape[0]
+        E = self.n_experts
         if not self.grouped(step, T):
-            a = self.gate_up(xin, mode=SWIGLU)
-            K.scale_column_blocks(a, dense, self.ff, self.n_experts)
+            a = self._first(self.gate_up, xin)
+            K.scale_column_blocks(a, dense, self.ff, E)
+            if self.w_gate is not None:                   # the shared expert's stretch times the token's gate
+                K.scale_column_blocks(a[:, E * self.ff:], dense[:, E:], self.shared_ff, 1)
             self.down(a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
             return
         counts, order, where = K.moe_group(chosen, self.n_experts)
@@ -140,10 +180,12 @@ class RoutedExperts(FeedForward):
         at = 0
         for e, n in enumerate(counts):
             if n:
-                a = self.gate_up_of[e](rows[at:at + n], mode=SWIGLU)
+                a = self._first(self.gate_up_of[e], rows[at:at + n])
                 self.down_of[e](a, out=outs[at:at + n], mode=STORE_F32)
                 at += n
         if self.shared_ff:
-            a = self.gate_up_of[self.n_experts](xin, mode=SWIGLU)
-            self.down_of[self.n_experts](a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
+            a = self._first(self.gate_up_of[E], xin)
+            if self.w_gate is not None:
+                K.scale_column_blocks(a, dense[:, E:], self.shared_ff, 1)
+            self.down_of[E](a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
         K.moe_combine(outs, where, weights, residual, accumulate=bool(self.shared_ff) or not store)
