@@ -2,9 +2,10 @@ from .base import ConfigError, KeyReader, ModelConfig, read_config_json
 from .dabodra import DabodraConfig
 from .llama import LlamaConfig, RopeScaling
 from .nibelorn import NibelornConfig
+from .vitinex import VitinexConfig
 from .registry import (Architecture, architecture_name, find_architecture, register_architecture,
                        registered_architectures)
 
-__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling", "NibelornConfig", "DabodraConfig",
+__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling", "NibelornConfig", "DabodraConfig", "VitinexConfig",
            "Architecture", "architecture_name", "find_architecture", "register_architecture",
            "registered_architectures"]

@@ -216,11 +216,11 @@ def gelu(x: torch.Tensor, kind: int = GELU_ERF) -> None:
     _check(f(_ptr(x), dtype_code(x.dtype), x.shape[0], x.shape[1], x.stride(0), kind, _stream()), "gelu")
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r][j] = silu(gu[r][2j]) * gu[r][2j+1]."""
+def swiglu(gu: torch.Tensor, out: torch.Tensor, act: int = 0) -> None:
+    """out[r][j] = silu(gu[r][2j]) * gu[r][2j+1]; with act (ACT_*), that activation takes silu's place."""
     _need(gu, "gu"); _need(out, "out", gu.dtype)
-    f = _fn("elementwise", "stratum_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gu), _ptr(out), dtype_code(gu.dtype), out.shape[0], out.shape[1], _stream()), "swiglu")
+    f = _fn("elementwise", "stratum_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gu), _ptr(out), dtype_code(gu.dtype), out.shape[0], out.shape[1], int(act), _stream()), "swiglu")
 
 
 def rope_store(qkv: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
@@ -271,7 +271,8 @@ EPI_STORE, EPI_ADD_F32, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3
 EPI_ADD_F32_EMIT, EPI_QKV_ROPE = 4, 5          # gemm_tc only: see GemmExtra
 
 
-ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2       # what a product with EPI_STORE may apply to what it stores
+# what a product with EPI_STORE may apply to what it stores; with EPI_SWIGLU: the gate's activation (0 = silu)
+ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_RELU_SQ = 0, 1, 2, 3
 
 
 def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -536,7 +537,7 @@ class _MixerPrep(ctypes.Structure):
                 ("n_v", c_int), ("v_dim", c_int), ("v_col", c_int),
                 ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float),
                 ("q_out_ld", c_int), ("q_out_step", c_int), ("q_out_off", c_int), ("k_out_ld", c_int),
-                ("reserved", c_int)]
+                ("interleaved", c_int)]
 
 
 def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
@@ -544,10 +545,10 @@ def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor
                *, queries=(0, 0, 0), keys=(0, 0, 0), values=(0, 0, 0), inv_freq: Optional[torch.Tensor] = None,
                q_rot_off: int = 0, k_rot_off: int = 0, k_norm_gain: Optional[torch.Tensor] = None,
                eps: float = 0.0, q_out: Optional[torch.Tensor] = None, q_out_step: int = 0,
-               q_out_off: int = 0, k_out: Optional[torch.Tensor] = None) -> None:
+               q_out_off: int = 0, k_out: Optional[torch.Tensor] = None, interleaved: bool = False) -> None:
     """Between a fused projection and attention.  x [tokens, ld] holds runs of equal heads: queries, keys, values,
     each given as (heads, head size, first column).  Queries: dimensions [q_rot_off, q_rot_off + 2R) rotated in
-    place (R = len(inv_freq), pairs (i, i + R)); with q_out [tokens, *] the dimensions from q_rot_off on go, the
+    place (R = len(inv_freq), pairs (i, i + R), or the neighbours (2i, 2i + 1) when `interleaved`); with q_out [tokens, *] the dimensions from q_rot_off on go, the
     first 2R rotated, to q_out[:, j * q_out_step + q_out_off ...] for head j instead.  Keys: the first len(k_norm_gain) dimensions divided by their
     root mean square (eps inside the root) times the gain, dimensions [k_rot_off, k_rot_off + 2R) rotated, then
     appended to k_cache, and with k_out [tokens, *] also written to its row t (zeros for tokens of no sequence).
@@ -561,6 +562,7 @@ def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor
     p.n_k, p.k_dim, p.k_col = keys
     p.n_v, p.v_dim, p.v_col = values
     p.q_rot_off, p.k_rot_off = q_rot_off, k_rot_off
+    p.interleaved = int(bool(interleaved))
     if inv_freq is not None:
         _need(inv_freq, "inv_freq", torch.float32)
         p.inv_freq, p.rot_pairs = inv_freq.data_ptr(), inv_freq.numel()
@@ -587,6 +589,19 @@ def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor
             p.v_cache = v_cache.data_ptr()
     f = _fn("mixer_prep", "stratum_mixer_prep", [c_void_p, c_int, c_void_p])
     _check(f(ctypes.addressof(p), dtype_code(x.dtype), _stream()), "mixer_prep")
+
+
+def gate_heads(a: torch.Tensor, g: torch.Tensor, n_heads: int, block: int) -> None:
+    """In place: a[t, j * block + i] *= sigmoid(g[t, j]) for j < n_heads, i < block; a and g of one dtype, rows of
+    any stride."""
+    _need(a, "a", contiguous=False); _need(g, "g", a.dtype, contiguous=False)
+    if a.shape[0] != g.shape[0] or a.shape[1] < n_heads * block or g.shape[1] < n_heads or a.stride(1) != 1 \
+            or g.stride(1) != 1:
+        raise KernelError("gate_heads: shapes disagree")
+    f = _fn("mixer_prep", "stratum_gate_heads",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(g), g.stride(0), a.shape[0], n_heads, block, dtype_code(a.dtype), _stream()),
+           "gate_heads")
 
 
 class _GeneralAttention(ctypes.Structure):
@@ -751,6 +766,58 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_ptr(x), _ptr(out), x.numel(), _stream()), "cast_rows")
 
 
+# ------------------------------------------------------------------ layer norm (weight, no bias)
+def layernorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (v - mean v) / sqrt(var v + eps) * gain with v = x[rows[r]] or x[r].  x float32 [*, H], gain float32
+    [H], out [rows, H] float32 or bfloat16."""
+    _need(x, "x", torch.float32); _need(gain, "gain", torch.float32); _need(out, "out")
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n_rows:
+            raise KernelError("layernorm: rows and out disagree")
+    elif x.shape[0] != n_rows:
+        raise KernelError("layernorm: x and out disagree")
+    if gain.numel() != x.shape[-1] or out.shape[-1] != x.shape[-1]:
+        raise KernelError("layernorm: gain, x and out disagree")
+    f = _fn("layer_norm", "stratum_layernorm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(x), _ptr(gain), _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows, x.shape[-1], c_float(eps),
+             _stream()), "layernorm")
+
+
+def layernorm_into_residual(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor,
+                            accumulate: bool = True, next_gain: Optional[torch.Tensor] = None,
+                            next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> None:
+    """x[r] (+)= layer norm of y[r] times gain, float32 [rows, H] both; with next_out [rows, H] (float32 or
+    bfloat16) also next_out[r] = layer norm of the new x[r] times next_gain: the norm in front of the next sublayer."""
+    _need(y, "y", torch.float32); _need(x, "x", torch.float32); _need(gain, "gain", torch.float32)
+    if y.shape != x.shape or gain.numel() != x.shape[-1]:
+        raise KernelError("layernorm_into_residual: y, x and gain disagree")
+    code = 0
+    if next_out is not None:
+        _need(next_out, "next_out"); _need(next_gain, "next_gain", torch.float32)
+        if next_out.shape != x.shape or next_gain.numel() != x.shape[-1]:
+            raise KernelError("layernorm_into_residual: next_out, next_gain and x disagree")
+        code = dtype_code(next_out.dtype)
+    f = _fn("layer_norm", "stratum_layernorm_into_residual",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(gain), _ptr(x), _ptr(next_gain if next_out is not None else None), _ptr(next_out), code,
+             x.shape[0], x.shape[1], c_float(eps), c_float(next_eps), int(bool(accumulate)), _stream()),
+           "layernorm_into_residual")
+
+
+def pack_columns(x: torch.Tensor, out: torch.Tensor, col0: int) -> None:
+    """out[:, col0 : col0 + W] = x, rounded to out's dtype.  x float32 [rows, W] contiguous; out [rows, >= col0 + W]."""
+    _need(x, "x", torch.float32); _need(out, "out", contiguous=False)
+    if out.shape[0] != x.shape[0] or out.stride(1) != 1 or col0 < 0 or col0 + x.shape[1] > out.shape[1]:
+        raise KernelError("pack_columns: shapes disagree")
+    f = _fn("layer_norm", "stratum_pack_columns", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(out), dtype_code(out.dtype), x.shape[0], x.shape[1], out.stride(0), col0, _stream()),
+           "pack_columns")
+
+
 class _QKNormRope(ctypes.Structure):
     """Mirror of struct QKNormRope in csrc/qk_norm_rope.cu."""
     _fields_ = [("proj", c_void_p), ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
@@ -840,6 +907,58 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
     count_launches(2)
 
 
+# ------------------------------------------------------------------ the selective state-space mixer
+class _SsmScan(ctypes.Structure):
+    """Mirror of struct SsmScan in csrc/ssm_scan.cu."""
+    _fields_ = [("proj", c_void_p), ("conv_w", c_void_p), ("conv_b", c_void_p), ("a_log", c_void_p),
+                ("dt_bias", c_void_p), ("d_skip", c_void_p), ("gain", c_void_p), ("act", c_void_p),
+                ("y_raw", c_void_p), ("out", c_void_p), ("state", c_void_p),
+                ("token_pos", c_void_p), ("token_seq", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p),
+                ("ld", c_int), ("lda", c_int), ("ldo", c_int), ("n_tokens", c_int), ("n_seqs", c_int),
+                ("n_heads", c_int), ("vdim", c_int), ("n_state", c_int), ("n_groups", c_int), ("taps", c_int),
+                ("norm_groups", c_int), ("state_stride", c_int), ("write_state", c_int), ("eps", c_float)]
+
+
+def ssm_scan(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, a_log: torch.Tensor,
+             dt_bias: torch.Tensor, d_skip: torch.Tensor, gain: torch.Tensor, act: torch.Tensor, y_raw: torch.Tensor,
+             out: torch.Tensor, state: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+             seq_start: torch.Tensor, seq_slot: torch.Tensor, n_heads: int, vdim: int, n_state: int, n_groups: int,
+             norm_groups: int, eps: float, write_state: bool) -> None:
+    """One step of the selective state-space mixer for every sequence of the step (see csrc/ssm_scan.cu).  With inner
+    = n_heads vdim and C = inner + 2 n_groups n_state: proj float32 [tokens, >= inner + C + n_heads] ([z | x | B | C |
+    dt]); conv_w float32 [C, taps], conv_b [C]; a_log, dt_bias, d_skip [n_heads]; gain [inner]; act [tokens, >= C + 2
+    n_heads] and y_raw [tokens, inner] float32 scratch; out [tokens, >= inner] in the compute dtype; state float32
+    [slots, inner n_state + (taps - 1) C]."""
+    for name, t in (("proj", proj), ("act", act)):
+        _need(t, name, torch.float32, contiguous=False)
+    for name, t in (("conv_w", conv_w), ("conv_b", conv_b), ("a_log", a_log), ("dt_bias", dt_bias),
+                    ("d_skip", d_skip), ("gain", gain), ("y_raw", y_raw), ("state", state)):
+        _need(t, name, torch.float32)
+    for name, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_start", seq_start),
+                    ("seq_slot", seq_slot)):
+        _need(t, name, torch.int32)
+    _need(out, "out", contiguous=False)
+    inner = n_heads * vdim
+    C = inner + 2 * n_groups * n_state
+    if conv_w.shape[0] != C or conv_b.numel() != C or gain.numel() != inner or a_log.numel() != n_heads \
+            or dt_bias.numel() != n_heads or d_skip.numel() != n_heads:
+        raise KernelError("ssm_scan: weights and sizes disagree")
+    if y_raw.numel() < proj.shape[0] * inner or out.shape[0] != proj.shape[0]:
+        raise KernelError("ssm_scan: buffers and tokens disagree")
+    p = _SsmScan()
+    p.proj, p.conv_w, p.conv_b, p.a_log = proj.data_ptr(), conv_w.data_ptr(), conv_b.data_ptr(), a_log.data_ptr()
+    p.dt_bias, p.d_skip, p.gain = dt_bias.data_ptr(), d_skip.data_ptr(), gain.data_ptr()
+    p.act, p.y_raw, p.out, p.state = act.data_ptr(), y_raw.data_ptr(), out.data_ptr(), state.data_ptr()
+    p.token_pos, p.token_seq, p.seq_start, p.seq_slot = (token_pos.data_ptr(), token_seq.data_ptr(),
+                                                         seq_start.data_ptr(), seq_slot.data_ptr())
+    p.ld, p.lda, p.ldo, p.n_tokens, p.n_seqs = proj.stride(0), act.stride(0), out.stride(0), proj.shape[0], seq_slot.numel()
+    p.n_heads, p.vdim, p.n_state, p.n_groups, p.taps = n_heads, vdim, n_state, n_groups, conv_w.shape[1]
+    p.norm_groups, p.state_stride, p.write_state, p.eps = norm_groups, state.stride(0), int(bool(write_state)), float(eps)
+    f = _fn("ssm_scan", "stratum_ssm_scan", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(out.dtype), _stream()), "ssm_scan")
+    count_launches(2)
+
+
 # ------------------------------------------------------------------ routed experts
 class _MoeRoute(ctypes.Structure):
     """Mirror of struct MoeRoute in csrc/moe_router.cu."""
@@ -847,23 +966,34 @@ class _MoeRoute(ctypes.Structure):
                 ("chosen", c_void_p), ("weights", c_void_p),
                 ("ldx", c_int), ("ldd", c_int), ("n_tokens", c_int), ("width", c_int),
                 ("n_experts", c_int), ("top", c_int), ("n_groups", c_int), ("keep", c_int),
-                ("scale", c_float), ("reserved", c_float)]
+                ("scale", c_float), ("reserved", c_float), ("w_gate", c_void_p), ("score", c_int), ("renorm", c_int)]
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, dense: torch.Tensor,
-              chosen: torch.Tensor, weights: torch.Tensor, top: int, n_groups: int, keep: int, scale: float) -> None:
-    """Sigmoid routing with a choice correction and groups (see csrc/moe_router.cu).  x [tokens, width] float32 or
-    bfloat16; w_router float32 [experts, width]; correction float32 [experts]; dense float32 [tokens, >= experts]
-    (weights, zeros for experts not chosen); chosen int32 and weights float32 [tokens, top]."""
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], dense: torch.Tensor,
+              chosen: torch.Tensor, weights: torch.Tensor, top: int, n_groups: int, keep: int, scale: float,
+              softmax: bool = False, renorm: bool = True, w_gate: Optional[torch.Tensor] = None) -> None:
+    """Routing with a choice correction and groups (see csrc/moe_router.cu): scores by sigmoid, or by softmax over all
+    experts; the chosen scores divided by their sum (renorm) or left as they are.  x [tokens, width] float32 or
+    bfloat16; w_router float32 [experts, width]; correction float32 [experts] or None; dense float32 [tokens, >=
+    experts] (weights, zeros for experts not chosen); chosen int32 and weights float32 [tokens, top].  w_gate
+    float32 [width]: dense[:, experts] receives sigmoid(x . w_gate), the gate of a shared expert."""
     _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32)
-    _need(correction, "correction", torch.float32); _need(dense, "dense", torch.float32, contiguous=False)
+    _need(dense, "dense", torch.float32, contiguous=False)
     _need(chosen, "chosen", torch.int32); _need(weights, "weights", torch.float32)
     E = w_router.shape[0]
-    if w_router.shape[1] != x.shape[1] or correction.numel() != E or chosen.shape != (x.shape[0], top) \
-            or weights.shape != (x.shape[0], top) or dense.shape[0] != x.shape[0]:
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+    if w_router.shape[1] != x.shape[1] or (correction is not None and correction.numel() != E) \
+            or chosen.shape != (x.shape[0], top) or weights.shape != (x.shape[0], top) or dense.shape[0] != x.shape[0]:
         raise KernelError("moe_route: shapes disagree")
     p = _MoeRoute()
-    p.x, p.w_router, p.correction = x.data_ptr(), w_router.data_ptr(), correction.data_ptr()
+    p.x, p.w_router, p.correction = x.data_ptr(), w_router.data_ptr(), (0 if correction is None else correction.data_ptr())
+    p.score, p.renorm = int(bool(softmax)), int(bool(renorm))
+    if w_gate is not None:
+        _need(w_gate, "w_gate", torch.float32)
+        if w_gate.numel() != x.shape[1] or dense.shape[1] < E + 1:
+            raise KernelError("moe_route: the shared gate needs one row of weights and one more column of dense")
+        p.w_gate = w_gate.data_ptr()
     p.dense, p.chosen, p.weights = dense.data_ptr(), chosen.data_ptr(), weights.data_ptr()
     p.ldx, p.ldd, p.n_tokens, p.width = x.stride(0), dense.stride(0), x.shape[0], x.shape[1]
     p.n_experts, p.top, p.n_groups, p.keep, p.scale = E, top, n_groups, keep, float(scale)
