@@ -5,6 +5,7 @@
     python bench.py --impl reference        # the reference arm (see below)
     python bench.py --compare nibelorn      # the Nibelorn decoder beside a Llama decoder of equal size (one JSON line)
     python bench.py --compare dabodra       # the same for the Dabodra decoder
+    python bench.py --compare vitinex       # the Vitinex decoder beside the Dabodra and the Llama decoder of equal size
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
 sequence's cache filled to the given context at the end of the timed steps (so the timed steps
@@ -110,6 +111,37 @@ def dabodra_config(size, n_layers):
                                     "norm": {"eps": 1e-5}, "layers": layers})
 
 
+# --compare vitinex: the same widths, heads and vocabulary as Dabodra's sizes, beside the Dabodra decoder (the closest
+# one here: recurrent layers of fixed state between attention layers, routed experts) and the Llama decoder.  Three
+# state-space layers (inner size twice the width, heads of 64, a state of 128) to one layer of latent attention with a
+# query latent; eight ungated squared-ReLU experts of which a token uses two, and a gated shared expert, sized so that
+# a token's active feed-forward weights equal the Llama decoder's SwiGLU (2 x (2 x ff + shared) = 3 x llama_inner).
+# The whole stack is one loop that runs once: the re-entry product is part of every step.
+VITINEX_SIZES = {
+    "1b": {"latent": {"dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 768},
+           "ssm": {"vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8},
+           "experts": 8, "top": 2, "ff": 2048, "shared": 4160},
+    "8b": {"latent": {"dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536},
+           "ssm": {"vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8},
+           "experts": 8, "top": 2, "ff": 4096, "shared": 8128},
+}
+
+
+def vitinex_config(size, n_layers):
+    from stratum_b200.config import VitinexConfig
+    z, v = COMPARE_SIZES[size], VITINEX_SIZES[size]
+    lat = dict(v["latent"], heads=z["heads"], scale=(v["latent"]["dim"] + v["latent"]["rot_dim"]) ** -0.5,
+               rot={"base": 10000.0, "dims": v["latent"]["rot_dim"]})
+    ssm = dict(v["ssm"], heads=2 * z["width"] // v["ssm"]["vdim"])
+    mlp = {"kind": "moe", "router": {"experts": v["experts"], "top": v["top"]}, "expert": {"ff": v["ff"]},
+           "shared": {"ff": v["shared"]}}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": mlp} if i % 4 == 3 else
+              {"type": "mamba2", "mixer": ssm, "mlp": mlp} for i in range(n_layers)]
+    return VitinexConfig.from_dict({"architecture": "Vitinex", "vocab": z["vocab"], "width": z["width"],
+                                    "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers,
+                                    "loop": {"start": 0, "stop": n_layers, "times": 1}})
+
+
 def llama_like(size, n_layers):
     from stratum_b200.config import LlamaConfig
     z = COMPARE_SIZES[size]
@@ -149,7 +181,8 @@ def kernel_times(llm, batch, context, prefill_tokens, vocab, rng):
 
 
 def compare_models(args, rng):
-    """Prefill and decode throughput of the Nibelorn or the Dabodra decoder beside a Llama decoder of equal size: one
+    """Prefill and decode throughput of the Nibelorn, the Dabodra or the Vitinex decoder beside a Llama decoder of equal
+    size (the Vitinex decoder also beside the Dabodra decoder): one
     prompt of --prefill-tokens, and decode steps of --batch sequences at --context tokens (random bf16 weights,
     device-timed as the main workload is); with --kernels also the device time of every kernel of one prompt and one
     decode step.  One JSON line."""
@@ -157,13 +190,14 @@ def compare_models(args, rng):
     from stratum_b200 import Stratum
     n_layers = args.layers or 8
     which = args.compare
-    make = nibelorn_config if which == "nibelorn" else dabodra_config
+    make = {"nibelorn": nibelorn_config, "dabodra": dabodra_config, "vitinex": vitinex_config}[which]
+    others = [("llama", llama_like)] + ([("dabodra", dabodra_config)] if which == "vitinex" else [])
     out = {"compare": which, "layers": n_layers, "batch": args.batch, "context": args.context,
            "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic: random-init weights",
            "sizes": {}}
     for size in sorted(COMPARE_SIZES):
         row = {}
-        for name, cfg in ((which, make(size, n_layers)), ("llama", llama_like(size, n_layers))):
+        for name, cfg in [(which, make(size, n_layers))] + [(n, f(size, n_layers)) for n, f in others]:
             llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
                                       max_tokens=max(args.batch * (args.context + 64), args.prefill_tokens + 64),
                                       max_seqs=args.batch)
@@ -180,6 +214,9 @@ def compare_models(args, rng):
             torch.cuda.empty_cache()
         row["decode_ratio"] = round(row[which]["decode_tok_per_s"] / row["llama"]["decode_tok_per_s"], 3)
         row["prefill_ratio"] = round(row[which]["prefill_tok_per_s"] / row["llama"]["prefill_tok_per_s"], 3)
+        for n, _ in others[1:]:
+            row[f"decode_ratio_{n}"] = round(row[which]["decode_tok_per_s"] / row[n]["decode_tok_per_s"], 3)
+            row[f"prefill_ratio_{n}"] = round(row[which]["prefill_tok_per_s"] / row[n]["prefill_tok_per_s"], 3)
         out["sizes"][size] = row
     print(json.dumps(out))
     return 0
@@ -412,9 +449,9 @@ def main() -> int:
                     help="prompt length of --prefill-only (the default JSON line always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
-    ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra"],
-                    help="instead of the main workload: prefill and decode throughput of the Nibelorn or the Dabodra "
-                         "decoder beside a Llama decoder of equal size, at 1B-like and 8B-like layer sizes (--layers of "
+    ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra", "vitinex"],
+                    help="instead of the main workload: prefill and decode throughput of the Nibelorn, the Dabodra or "
+                         "the Vitinex decoder beside a Llama decoder of equal size (Vitinex also beside Dabodra), at 1B-like and 8B-like layer sizes (--layers of "
                          "them, default 8)")
     ap.add_argument("--kernels", action="store_true",
                     help="with --compare: also the device time of every kernel of one prompt and one decode step")

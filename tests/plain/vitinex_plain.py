@@ -164,20 +164,25 @@ def squared_relu_expert(h, up, down):
     return linear(a * a, down)
 
 
-def route_softmax(h, router, top):
-    """(chosen [T, top], their scores [T, top]): the largest softmax scores, lower index first among equals."""
+def route_softmax(h, router, top, margins: Optional[list] = None):
+    """(chosen [T, top], their scores [T, top]): the largest softmax scores, lower index first among equals.
+    margins (a list) receives, per token, the gap between the last chosen logit and the best one left out."""
     z = linear(h, router)
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z)
     s = s / s.sum(axis=-1, keepdims=True)
-    order = np.argsort(-s, axis=-1, kind="stable")[:, :top]
+    full = np.argsort(-s, axis=-1, kind="stable")
+    order = full[:, :top]
+    if margins is not None and top < z.shape[-1]:
+        rows = np.arange(z.shape[0])
+        margins.extend((z[rows, full[:, top - 1]] - z[rows, full[:, top]]).tolist())
     return order, np.take_along_axis(s, order, axis=-1)
 
 
-def routed_experts(h, w: Dict[str, np.ndarray], f: dict):
+def routed_experts(h, w: Dict[str, np.ndarray], f: dict, margins: Optional[list] = None):
     T = h.shape[0]
     E, top = f["router"]["experts"], f["router"]["top"]
-    chosen, score = route_softmax(h, w["router"], top)
+    chosen, score = route_softmax(h, w["router"], top, margins)
     out = np.zeros((T, np.asarray(w["e0.down"]).shape[0]), F64)
     for t in range(T):
         for k in range(top):
@@ -195,7 +200,7 @@ def sub(weights: Dict[str, np.ndarray], prefix: str) -> Dict[str, np.ndarray]:
     return {k[n:]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def layer_forward(x, weights, cfg: dict, i: int):
+def layer_forward(x, weights, cfg: dict, i: int, margins: Optional[list] = None):
     L, eps, m = cfg["layers"][i], cfg["norm"]["eps"], F64(cfg["residual_mult"])
     p = f"l{i}."
     h = layer_norm(x, weights[p + "norm1"], eps)
@@ -207,7 +212,7 @@ def layer_forward(x, weights, cfg: dict, i: int):
     if L.get("mlp") is not None:
         h = layer_norm(x, weights[p + "norm2"], eps)
         f = L["mlp"]
-        y = dense_feed_forward(h, sub(weights, p + "mlp.")) if f["kind"] == "dense" else routed_experts(h, sub(weights, p + "mlp."), f)
+        y = dense_feed_forward(h, sub(weights, p + "mlp.")) if f["kind"] == "dense" else routed_experts(h, sub(weights, p + "mlp."), f, margins)
         x = x + m * layer_norm(y, weights[p + "norm2b"], eps)
     return x
 
@@ -224,14 +229,16 @@ def layer_runs(cfg: dict) -> List[tuple]:
     return runs + [(i, None, False) for i in range(loop["stop"], n)]
 
 
-def forward(tokens, weights: Dict[str, np.ndarray], cfg: dict, streams: Optional[list] = None):
-    """Logits [T, vocab] of one whole sequence; streams (a list) receives the residual stream after every layer run."""
+def forward(tokens, weights: Dict[str, np.ndarray], cfg: dict, streams: Optional[list] = None,
+            margins: Optional[list] = None):
+    """Logits [T, vocab] of one whole sequence; streams (a list) receives the residual stream after every layer run,
+    margins the routers' gaps between the last expert chosen and the first left out (in logits)."""
     x0 = np.asarray(weights["embed"], F64)[np.asarray(tokens)]
     x = x0.copy()
     for i, t, first in layer_runs(cfg):
         if first:
             x = linear(np.concatenate([x, x0], axis=-1), weights["loop.in"]) + np.asarray(weights["loop.step"], F64)[t]
-        x = layer_forward(x, weights, cfg, i)
+        x = layer_forward(x, weights, cfg, i, margins)
         if streams is not None:
             streams.append(x.copy())
     return linear(layer_norm(x, weights["final.norm"], cfg["norm"]["eps"]), weights["embed"])
