@@ -45,13 +45,25 @@ struct SsmScan {
 
 __device__ __forceinline__ float ss_silu(float z) { return z / (1.0f + expf(-z)); }
 
-// ---------------------------------------------------------------- prep: one block per token
+// ---------------------------------------------------------------- prep: a block per (token, stretch of channels)
 #define SS_PREP_THREADS 256
 __global__ void __launch_bounds__(SS_PREP_THREADS) ssm_prep_kernel(const SsmScan P) {
   pdl_trigger();
   pdl_wait();                // the projection and the state are the work of kernels before this one: ld_fresh
   const int t = blockIdx.x;
   const int inner = P.n_heads * P.vdim, C = inner + 2 * P.n_groups * P.n_state;
+  const int item = blockIdx.y * SS_PREP_THREADS + threadIdx.x;      // a channel, or behind the channels a head
+  if (item >= C + P.n_heads) return;
+  float* out = P.act + (size_t)t * P.lda;
+  if (item >= C) {
+    const int h = item - C;
+    const float z = ld_fresh(P.proj + (size_t)t * P.ld + inner + C + h) + P.dt_bias[h];
+    const float dt = z > 20.f ? z : log1pf(expf(z));
+    out[C + h] = dt;
+    out[C + P.n_heads + h] = expf(-expf(P.a_log[h]) * dt);
+    return;
+  }
+  const int c = item;
   const int seq = P.token_seq[t], pos = P.token_pos[t];
   int in_step = 0;           // tokens of this sequence that the step brought before this one
   const float* tail = nullptr;
@@ -59,25 +71,16 @@ __global__ void __launch_bounds__(SS_PREP_THREADS) ssm_prep_kernel(const SsmScan
     in_step = t - P.seq_start[seq];
     tail = P.state + (size_t)P.seq_slot[seq] * P.state_stride + (size_t)inner * P.n_state;
   }
-  float* out = P.act + (size_t)t * P.lda;
   const int n = P.taps;
-  for (int c = threadIdx.x; c < C; c += SS_PREP_THREADS) {
-    const float* w = P.conv_w + (size_t)c * n;
-    float acc = P.conv_b[c];
-    for (int i = n - 1; i >= 0; i--) {               // oldest input first: one fixed order
-      float x = 0.f;
-      if (i <= in_step) x = ld_fresh(P.proj + (size_t)(t - i) * P.ld + inner + c);
-      else if (tail && pos - i >= 0) x = ld_fresh(tail + (size_t)(n - 1 - (i - in_step)) * C + c);
-      acc = fmaf(w[n - 1 - i], x, acc);
-    }
-    out[c] = ss_silu(acc);
+  const float* w = P.conv_w + (size_t)c * n;
+  float acc = P.conv_b[c];
+  for (int i = n - 1; i >= 0; i--) {                 // oldest input first: one fixed order
+    float x = 0.f;
+    if (i <= in_step) x = ld_fresh(P.proj + (size_t)(t - i) * P.ld + inner + c);
+    else if (tail && pos - i >= 0) x = ld_fresh(tail + (size_t)(n - 1 - (i - in_step)) * C + c);
+    acc = fmaf(w[n - 1 - i], x, acc);
   }
-  for (int h = threadIdx.x; h < P.n_heads; h += SS_PREP_THREADS) {
-    const float z = ld_fresh(P.proj + (size_t)t * P.ld + inner + C + h) + P.dt_bias[h];
-    const float dt = z > 20.f ? z : log1pf(expf(z));
-    out[C + h] = dt;
-    out[C + P.n_heads + h] = expf(-expf(P.a_log[h]) * dt);
-  }
+  out[c] = ss_silu(acc);
 }
 
 // ---------------------------------------------------------------- the recurrence
@@ -239,28 +242,49 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) 
   }
 }
 
-// ---------------------------------------------------------------- finish: one warp per (token, part of the row)
+// ---------------------------------------------------------------- finish: a block per (token, part of the row)
+// The sum of squares is added in an order that the part's size alone fixes: a thread over its strided entries, a
+// warp by shuffles, the warps one after another.
+#define SS_FIN_THREADS 128
 template <typename T>
-__global__ void __launch_bounds__(128) ssm_finish_kernel(const SsmScan P) {
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(SS_FIN_THREADS) ssm_finish_kernel(const SsmScan P) {
+  __shared__ float warp_ss[SS_FIN_THREADS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_trigger();
   pdl_wait();                // y_raw and the projection are the work of kernels before this one: ld_fresh
-  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= (long long)P.n_tokens * P.norm_groups) return;
+  const long long item = blockIdx.x;
   const int t = (int)(item / P.norm_groups), part = (int)(item - (long long)t * P.norm_groups);
   const int inner = P.n_heads * P.vdim, size = inner / P.norm_groups;
   const float* y = P.y_raw + (size_t)t * inner + (size_t)part * size;
   const float* z = P.proj + (size_t)t * P.ld + (size_t)part * size;
   const float* gain = P.gain + (size_t)part * size;
   T* out = (T*)P.out + (size_t)t * P.ldo + (size_t)part * size;
+  constexpr int KEEP = 4;    // entries a thread keeps between the two passes (parts of up to 512 are read once)
+  float kept[KEEP];
   float ss = 0.f;
-  for (int d = lane; d < size; d += 32) {
+#pragma unroll
+  for (int i = 0; i < KEEP; i++) {
+    const int d = threadIdx.x + i * SS_FIN_THREADS;
+    kept[i] = d < size ? ld_fresh(y + d) * ss_silu(ld_fresh(z + d)) : 0.f;
+    ss = fmaf(kept[i], kept[i], ss);
+  }
+  for (int d = threadIdx.x + KEEP * SS_FIN_THREADS; d < size; d += SS_FIN_THREADS) {
     const float v = ld_fresh(y + d) * ss_silu(ld_fresh(z + d));
     ss = fmaf(v, v, ss);
   }
   ss = warp_sum(ss);
-  const float mul = 1.0f / sqrtf(ss / (float)size + P.eps);
-  for (int d = lane; d < size; d += 32)
+  if (lane == 0) warp_ss[warp] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < SS_FIN_THREADS / 32; i++) total += warp_ss[i];
+  const float mul = 1.0f / sqrtf(total / (float)size + P.eps);
+#pragma unroll
+  for (int i = 0; i < KEEP; i++) {
+    const int d = threadIdx.x + i * SS_FIN_THREADS;
+    if (d < size) out[d] = from_float<T>(kept[i] * mul * gain[d]);
+  }
+  for (int d = threadIdx.x + KEEP * SS_FIN_THREADS; d < size; d += SS_FIN_THREADS)
     out[d] = from_float<T>(ld_fresh(y + d) * ss_silu(ld_fresh(z + d)) * mul * gain[d]);
 }
 
@@ -289,7 +313,11 @@ STRATUM_EXPORT int stratum_ssm_scan(const SsmScan* params, int out_dtype, cudaSt
   if (P.n_tokens <= 0 || P.n_seqs <= 0) return 0;
   const int bad = ssm_check(P);
   if (bad) return bad;
-  launch_pdl(ssm_prep_kernel, P.n_tokens, SS_PREP_THREADS, 0, stream, P);
+  {
+    const int inner = P.n_heads * P.vdim, items = inner + 2 * P.n_groups * P.n_state + P.n_heads;
+    launch_pdl(ssm_prep_kernel, dim3(P.n_tokens, (items + SS_PREP_THREADS - 1) / SS_PREP_THREADS), SS_PREP_THREADS, 0,
+               stream, P);
+  }
   int st = launch_status();
   if (st) return st;
   int L = 1;
@@ -304,11 +332,10 @@ STRATUM_EXPORT int stratum_ssm_scan(const SsmScan* params, int out_dtype, cudaSt
   }
   st = launch_status();
   if (st) return st;
-  const long long items = (long long)P.n_tokens * P.norm_groups;
-  const long long blocks = (items + 3) / 4;
+  const long long blocks = (long long)P.n_tokens * P.norm_groups;
   if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
-  if (out_dtype == STRATUM_DT_F32) launch_pdl(ssm_finish_kernel<float>, (unsigned)blocks, 128, 0, stream, P);
-  else if (out_dtype == STRATUM_DT_BF16) launch_pdl(ssm_finish_kernel<bf16>, (unsigned)blocks, 128, 0, stream, P);
+  if (out_dtype == STRATUM_DT_F32) launch_pdl(ssm_finish_kernel<float>, (unsigned)blocks, SS_FIN_THREADS, 0, stream, P);
+  else if (out_dtype == STRATUM_DT_BF16) launch_pdl(ssm_finish_kernel<bf16>, (unsigned)blocks, SS_FIN_THREADS, 0, stream, P);
   else return STRATUM_ERR_DTYPE;
   return launch_status();
 }
