@@ -13,8 +13,8 @@
 // All of it is float32 whatever the compute dtype.
 //
 // Every entry of S follows a recurrence of its own, so the work is independent across sequences, heads, columns and
-// rows of S and sequential only in time.  A block owns (sequence, head, a tile of columns), a thread 16 rows of one
-// column; the column's read-out is added over neighbouring lanes by shuffles in a fixed order.  The tokens' B, C, x,
+// rows of S and sequential only in time.  A block owns (sequence, head, a tile of columns), a thread a few rows of a
+// few columns; a column's read-out is added over neighbouring lanes by shuffles in a fixed order.  The tokens' B, C, x,
 // dt and decay come through a double buffer in shared memory (cp.async).  Nothing depends on how a sequence's
 // tokens are cut into steps, nor on the other sequences of a step.
 #include <math.h>
@@ -85,8 +85,8 @@ __global__ void __launch_bounds__(SS_PREP_THREADS) ssm_prep_kernel(const SsmScan
 
 // ---------------------------------------------------------------- the recurrence
 #define SS_THREADS 128
-#define SS_ROWS 16            // rows of a column of S that a lane holds
-#define SS_MAX_CHUNK 16       // tokens staged in shared memory at a time, at most
+#define SS_HELD 16            // entries of S that a lane holds: R rows of Q columns
+#define SS_MAX_CHUNK 8        // tokens staged in shared memory at a time, at most
 
 __device__ __forceinline__ void ss_copy4(float* dst_shared, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
@@ -100,29 +100,39 @@ __device__ __forceinline__ void ss_commit() { asm volatile("cp.async.commit_grou
 __device__ __forceinline__ void ss_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // The state of a head lies in memory column by column (S^T: [vdim][n_state]), so the rows a thread holds are
-// contiguous.  A column is spread over L lanes of SS_ROWS rows each (n_state <= SS_ROWS * L).
-template <int L>
+// contiguous.  A thread holds R rows of Q neighbouring columns (R Q = SS_HELD), and a group of L lanes covers the
+// rows of its Q columns (n_state <= R L).  A 16-byte load from shared memory costs a quarter-warp one pass however
+// many of its lanes share an address, so few rows per lane make every pass carry distinct words of B and C, and one
+// load serves Q columns.  Per token a lane only leaves the Q partial read-outs of its rows in shared memory; when a
+// chunk of tokens is through, the block adds them, a thread per (token, column), over the lanes in their order, with
+// the skip term.  So the loop over tokens has no exchange between lanes, and its only chain is the state's own.
+template <int L, int R>
 __global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) {
-  constexpr int ROWS = SS_ROWS;
-  constexpr int COLS = SS_THREADS / L;
-  constexpr int PITCH = 20;   // floats between two lanes' stretches of B and C: 16-byte aligned, banks spread
-  constexpr int BC = L * PITCH;
-  constexpr int FIT = 2048 / BC;
+  constexpr int Q = SS_HELD / R;
+  constexpr int COLS = SS_THREADS / L * Q;
+  constexpr int PITCH = R == 4 ? 4 : R + 4;          // floats between two lanes' stretches of B and C: 16-byte
+  constexpr int BC = L * PITCH;                      // aligned, and a quarter-warp's loads fall on distinct banks
+  constexpr int WIDEST = BC > COLS ? BC : COLS;
+  constexpr int FIT = 1024 / WIDEST;
   constexpr int CHUNK = FIT < 4 ? 4 : (FIT > SS_MAX_CHUNK ? SS_MAX_CHUNK : (FIT & ~3));
+  constexpr int GROUPS = SS_THREADS / L;
+  constexpr int PART_PITCH = (L + 1) * Q;            // floats between two groups' partial read-outs: banks spread
   __shared__ __align__(16) float bc_s[2][CHUNK][2][BC];
-  __shared__ float x_s[2][CHUNK][COLS];
-  __shared__ float dd_s[2][CHUNK][2];                // dt, decay
+  __shared__ __align__(16) float x_s[2][CHUNK][COLS];
+  __shared__ __align__(8) float dd_s[2][CHUNK][2];   // dt, decay
+  __shared__ __align__(16) float part_s[CHUNK][GROUPS][PART_PITCH];
   pdl_trigger();             // (launched the ordinary way itself: it starts when prep is done)
   const int seq = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
   const int r0 = P.seq_start[seq], r1 = P.seq_start[seq + 1];
   if (r0 >= r1) return;
   const int N = P.n_state, V = P.vdim, inner = P.n_heads * V, GN = P.n_groups * N, C = inner + 2 * GN;
-  const int part = threadIdx.x % L, col = threadIdx.x / L;
-  const int j = tile * COLS + col;
-  const bool live = j < V;
+  const int part = threadIdx.x % L, grp = threadIdx.x / L;
+  const int j0 = tile * COLS + grp * Q;              // the first of this lane's columns
   if (P.token_seq[r0] < 0) {                         // rows of no sequence: nothing is kept, the output is zero
-    if (part == 0 && live)
-      for (int r = r0; r < r1; r++) P.y_raw[(size_t)r * inner + (size_t)h * V + j] = 0.f;
+    if (part == 0)
+      for (int r = r0; r < r1; r++)
+        for (int q = 0; q < Q; q++)
+          if (j0 + q < V) P.y_raw[(size_t)r * inner + (size_t)h * V + j0 + q] = 0.f;
     return;
   }
   float* slot = P.state + (size_t)P.seq_slot[seq] * P.state_stride;
@@ -145,24 +155,30 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) 
 
   const int g = h / (P.n_heads / P.n_groups);
   const float d_skip = P.d_skip[h];
-  float* Sg = slot + ((size_t)h * V + (live ? j : 0)) * N + part * ROWS;
+  float* Sg = slot + ((size_t)h * V + j0) * N + part * R;              // column q of this lane: + q N
   const bool vec = N % 4 == 0 && (P.state_stride % 4) == 0 && (((uintptr_t)P.state) & 15) == 0;
-  float2 S[ROWS / 2];
+  float2 S[Q][R / 2];
 #pragma unroll
-  for (int i = 0; i < ROWS; i += 4) {
-    const int d = part * ROWS + i;
-    if (live && vec && d + 3 < N) {
-      const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
-      S[i / 2] = make_float2(v4.x, v4.y); S[i / 2 + 1] = make_float2(v4.z, v4.w);
-    } else {
-      float e[4];
+  for (int q = 0; q < Q; q++) {
+    const bool live = j0 + q < V;
 #pragma unroll
-      for (int u = 0; u < 4; u++) e[u] = (live && d + u < N) ? Sg[i + u] : 0.f;
-      S[i / 2] = make_float2(e[0], e[1]); S[i / 2 + 1] = make_float2(e[2], e[3]);
+    for (int i = 0; i < R; i += 4) {
+      const int d = part * R + i;
+      if (live && vec && d + 3 < N) {
+        const float4 v4 = *reinterpret_cast<const float4*>(Sg + (size_t)q * N + i);
+        S[q][i / 2] = make_float2(v4.x, v4.y); S[q][i / 2 + 1] = make_float2(v4.z, v4.w);
+      } else {
+        float e[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) e[u] = (live && d + u < N) ? Sg[(size_t)q * N + i + u] : 0.f;
+        S[q][i / 2] = make_float2(e[0], e[1]); S[q][i / 2 + 1] = make_float2(e[2], e[3]);
+      }
     }
   }
-  if (N != ROWS * L) {       // the rows beyond n_state in the staging buffers stay zero: nothing below writes them
+  // rows beyond n_state and columns beyond vdim stay zero in the staging buffers: nothing below writes them
+  if (N != R * L || (tile + 1) * COLS > V) {
     for (int i = threadIdx.x; i < 2 * CHUNK * 2 * BC; i += SS_THREADS) (&bc_s[0][0][0][0])[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * CHUNK * COLS; i += SS_THREADS) (&x_s[0][0][0])[i] = 0.f;
     __syncthreads();
   }
 
@@ -174,12 +190,12 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) 
       if (vec_act) {
         for (int d = 4 * threadIdx.x; d < 2 * N; d += 4 * SS_THREADS) {          // B, then C
           const int which = d >= N, dd = d - which * N;
-          ss_copy16(&bc_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + which * GN + dd);
+          ss_copy16(&bc_s[buf][tok][which][(dd / R) * PITCH + dd % R], a + which * GN + dd);
         }
       } else {
         for (int d = threadIdx.x; d < 2 * N; d += SS_THREADS) {
           const int which = d >= N, dd = d - which * N;
-          ss_copy4(&bc_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + which * GN + dd);
+          ss_copy4(&bc_s[buf][tok][which][(dd / R) * PITCH + dd % R], a + which * GN + dd);
         }
       }
     }
@@ -201,42 +217,76 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_recur_kernel(const SsmScan P) 
     __syncthreads();                                 // this chunk has landed, and the other buffer is free again
     if (c0 + CHUNK < r1) stage(buf ^ 1, c0 + CHUNK);
     const int n_here = min(CHUNK, r1 - c0);
-    float* y_row = P.y_raw + (size_t)c0 * inner + (size_t)h * V + (live ? j : 0);
-#pragma unroll 2
-    for (int tok = 0; tok < n_here; tok++, y_row += inner) {
+    auto token = [&](int tok) {                      // one token of the chunk: the state moves on, partials out
       const float4* bb = reinterpret_cast<const float4*>(&bc_s[buf][tok][0][part * PITCH]);
       const float4* cc = reinterpret_cast<const float4*>(&bc_s[buf][tok][1][part * PITCH]);
-      const float dt = dd_s[buf][tok][0], decay = dd_s[buf][tok][1];
-      const float xj = x_s[buf][tok][col];
-      const float dtx = dt * xj;
-      const float2 uu = make_float2(dtx, dtx), dk = make_float2(decay, decay);
-      float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+      float4 b4[R / 4], c4[R / 4];
 #pragma unroll
-      for (int i = 0; i < ROWS / 4; i++) {
-        const float4 b4 = bb[i], c4 = cc[i];
-        S[2 * i] = __ffma2_rn(make_float2(b4.x, b4.y), uu, __fmul2_rn(dk, S[2 * i]));
-        S[2 * i + 1] = __ffma2_rn(make_float2(b4.z, b4.w), uu, __fmul2_rn(dk, S[2 * i + 1]));
-        a0 = __ffma2_rn(S[2 * i], make_float2(c4.x, c4.y), a0);
-        a1 = __ffma2_rn(S[2 * i + 1], make_float2(c4.z, c4.w), a1);
+      for (int i = 0; i < R / 4; i++) { b4[i] = bb[i]; c4[i] = cc[i]; }
+      const float2 dd = *reinterpret_cast<const float2*>(&dd_s[buf][tok][0]);
+      const float2 dk = make_float2(dd.y, dd.y);
+      float xq[Q], y[Q];
+      if constexpr (Q == 4) {
+        const float4 x4 = *reinterpret_cast<const float4*>(&x_s[buf][tok][grp * Q]);
+        xq[0] = x4.x; xq[1] = x4.y; xq[2] = x4.z; xq[3] = x4.w;
+      } else if constexpr (Q == 2) {
+        const float2 x2 = *reinterpret_cast<const float2*>(&x_s[buf][tok][grp * Q]);
+        xq[0] = x2.x; xq[1] = x2.y;
+      } else {
+        xq[0] = x_s[buf][tok][grp];
       }
-      const float2 s2 = __fadd2_rn(a0, a1);
-      float y = s2.x + s2.y;
 #pragma unroll
-      for (int o = 1; o < L; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (part == 0 && live) *y_row = fmaf(d_skip, xj, y);
+      for (int q = 0; q < Q; q++) {
+        const float dtx = dd.x * xq[q];
+        const float2 uu = make_float2(dtx, dtx);
+        float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+#pragma unroll
+        for (int i = 0; i < R / 4; i++) {
+          S[q][2 * i] = __ffma2_rn(make_float2(b4[i].x, b4[i].y), uu, __fmul2_rn(dk, S[q][2 * i]));
+          S[q][2 * i + 1] = __ffma2_rn(make_float2(b4[i].z, b4[i].w), uu, __fmul2_rn(dk, S[q][2 * i + 1]));
+          a0 = __ffma2_rn(S[q][2 * i], make_float2(c4[i].x, c4[i].y), a0);
+          a1 = __ffma2_rn(S[q][2 * i + 1], make_float2(c4[i].z, c4[i].w), a1);
+        }
+        const float2 s2 = __fadd2_rn(a0, a1);
+        y[q] = s2.x + s2.y;
+      }
+      float* mine = &part_s[tok][grp][part * Q];
+      if constexpr (Q == 4) *reinterpret_cast<float4*>(mine) = make_float4(y[0], y[1], y[2], y[3]);
+      else if constexpr (Q == 2) *reinterpret_cast<float2*>(mine) = make_float2(y[0], y[1]);
+      else *mine = y[0];
+    };
+    if (n_here == CHUNK) {                           // a whole chunk: the tokens' loads and sums interleave
+#pragma unroll
+      for (int tok = 0; tok < CHUNK; tok++) token(tok);
+    } else {
+      for (int tok = 0; tok < n_here; tok++) token(tok);
+    }
+    __syncthreads();                                 // the chunk's partial read-outs are all there
+    for (int o = threadIdx.x; o < n_here * COLS; o += SS_THREADS) {
+      const int tok = o / COLS, c = o - tok * COLS;
+      const float* p = &part_s[tok][c / Q][c % Q];
+      float y = 0.f;
+#pragma unroll
+      for (int l = 0; l < L; l++) y += p[l * Q];
+      if (tile * COLS + c < V)
+        P.y_raw[(size_t)(c0 + tok) * inner + (size_t)h * V + tile * COLS + c] = fmaf(d_skip, x_s[buf][tok][c], y);
     }
   }
-  if (P.write_state && live) {
+  if (P.write_state) {
 #pragma unroll
-    for (int i = 0; i < ROWS; i += 4) {
-      const int d = part * ROWS + i;
-      const float e[4] = {S[i / 2].x, S[i / 2].y, S[i / 2 + 1].x, S[i / 2 + 1].y};
-      if (vec && d + 3 < N) {
-        *reinterpret_cast<float4*>(Sg + i) = make_float4(e[0], e[1], e[2], e[3]);
-      } else {
+    for (int q = 0; q < Q; q++) {
+      if (j0 + q >= V) continue;
 #pragma unroll
-        for (int u = 0; u < 4; u++)
-          if (d + u < N) Sg[i + u] = e[u];
+      for (int i = 0; i < R; i += 4) {
+        const int d = part * R + i;
+        const float e[4] = {S[q][i / 2].x, S[q][i / 2].y, S[q][i / 2 + 1].x, S[q][i / 2 + 1].y};
+        if (vec && d + 3 < N) {
+          *reinterpret_cast<float4*>(Sg + (size_t)q * N + i) = make_float4(e[0], e[1], e[2], e[3]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; u++)
+            if (d + u < N) Sg[(size_t)q * N + i + u] = e[u];
+        }
       }
     }
   }
@@ -295,16 +345,16 @@ static int ssm_check(const SsmScan& P) {
   if (P.norm_groups < 1 || inner % P.norm_groups != 0) return STRATUM_ERR_SHAPE;
   if (P.ld < inner + C + P.n_heads || P.lda < C + 2 * P.n_heads || P.ldo < inner) return STRATUM_ERR_SHAPE;
   if ((long long)P.state_stride < (long long)inner * P.n_state + (long long)(P.taps - 1) * C) return STRATUM_ERR_SHAPE;
-  if (P.n_state > 32 * SS_ROWS) return STRATUM_ERR_LIMIT;
+  if (P.n_state > 32 * SS_HELD) return STRATUM_ERR_LIMIT;
   if (P.n_heads > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
   return 0;
 }
 
-template <int L>
+template <int L, int R>
 static void ssm_recur_launch(const SsmScan& P, cudaStream_t stream) {
-  const int cols = SS_THREADS / L;
+  const int cols = SS_THREADS / L * (SS_HELD / R);
   const dim3 grid((P.vdim + cols - 1) / cols, P.n_heads, P.n_seqs);
-  ssm_recur_kernel<L><<<grid, SS_THREADS, 0, stream>>>(P);
+  ssm_recur_kernel<L, R><<<grid, SS_THREADS, 0, stream>>>(P);
 }
 
 // Everything of a step: prep, recurrence, finish (three launches).  out_dtype: the compute dtype of `out`.
@@ -320,15 +370,20 @@ STRATUM_EXPORT int stratum_ssm_scan(const SsmScan* params, int out_dtype, cudaSt
   }
   int st = launch_status();
   if (st) return st;
-  int L = 1;
-  while (SS_ROWS * L < P.n_state) L <<= 1;
-  switch (L) {
-    case 1: ssm_recur_launch<1>(P, stream); break;
-    case 2: ssm_recur_launch<2>(P, stream); break;
-    case 4: ssm_recur_launch<4>(P, stream); break;
-    case 8: ssm_recur_launch<8>(P, stream); break;
-    case 16: ssm_recur_launch<16>(P, stream); break;
-    default: ssm_recur_launch<32>(P, stream); break;
+  // few rows per lane while a warp still covers the rows: 4 up to 128 rows, 8 up to 256, 16 beyond
+  if (P.n_state > 256) ssm_recur_launch<32, 16>(P, stream);
+  else if (P.n_state > 128) ssm_recur_launch<32, 8>(P, stream);
+  else {
+    int L = 1;
+    while (4 * L < P.n_state) L <<= 1;
+    switch (L) {
+      case 1: ssm_recur_launch<1, 4>(P, stream); break;
+      case 2: ssm_recur_launch<2, 4>(P, stream); break;
+      case 4: ssm_recur_launch<4, 4>(P, stream); break;
+      case 8: ssm_recur_launch<8, 4>(P, stream); break;
+      case 16: ssm_recur_launch<16, 4>(P, stream); break;
+      default: ssm_recur_launch<32, 4>(P, stream); break;
+    }
   }
   st = launch_status();
   if (st) return st;
