@@ -22,64 +22,156 @@ __device__ __forceinline__ void ln_load(const float* src, float* row, int hidden
   }
 }
 
-// (mean, 1 / sqrt(var + eps)) of the row in shared memory; every thread gets both
+// Sum over the block with one barrier: the warps' sums go to `slots` (32 floats that nothing else uses in this
+// launch), and every thread adds them in the warps' order.
+__device__ __forceinline__ float ln_block_sum(float v, float* slots) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) slots[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < n_warps; w++) t += slots[w];
+  return t;
+}
+
+// (mean, 1 / sqrt(var + eps)) of the row in shared memory; every thread gets both.  scratch: 64 floats of its own.
+template <bool VEC>
 __device__ __forceinline__ float2 ln_stats(const float* row, int hidden, float eps, float* scratch) {
   float s = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) s += row[i];
-  const float mean = block_sum(s, scratch) / (float)hidden;
-  float q = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float d = row[i] - mean;
-    q = fmaf(d, d, q);
+  if (VEC) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(row)[i];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) s += row[i];
   }
-  const float var = block_sum(q, scratch) / (float)hidden;
+  const float mean = ln_block_sum(s, scratch) / (float)hidden;
+  float q = 0.f;
+  if (VEC) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(row)[i];
+      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+      q += fmaf(a, a, b * b) + fmaf(c, c, d * d);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = row[i] - mean;
+      q = fmaf(d, d, q);
+    }
+  }
+  const float var = ln_block_sum(q, scratch + 32) / (float)hidden;
   return make_float2(mean, 1.0f / sqrtf(var + eps));
+}
+
+// (v - mean) * rstd * gain for four neighbours
+__device__ __forceinline__ float4 ln_apply(float4 v, float2 st, float4 g) {
+  return make_float4((v.x - st.x) * st.y * g.x, (v.y - st.x) * st.y * g.y, (v.z - st.x) * st.y * g.z,
+                     (v.w - st.x) * st.y * g.w);
+}
+__device__ __forceinline__ void ln_store4(float* o, float4 v) { *reinterpret_cast<float4*>(o) = v; }
+__device__ __forceinline__ void ln_store4(bf16* o, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned*>(&lo);
+  u.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(o) = u;
 }
 
 template <typename T, bool VEC>
 __global__ void layernorm_kernel(const float* x, const float* __restrict__ gain, const int* __restrict__ rows, T* out,
                                  int hidden, float eps) {
   extern __shared__ __align__(16) float ln_row[];
-  __shared__ float scratch[33];
+  __shared__ float scratch[128];
   pdl_trigger();
   const int r = blockIdx.x;
   pdl_wait();                                        // x (and rows) are the work of kernels before this one
   const int src = rows ? __ldcg(rows + r) : r;
   ln_load<VEC>(x + (size_t)src * hidden, ln_row, hidden);
   __syncthreads();
-  const float2 st = ln_stats(ln_row, hidden, eps, scratch);
+  const float2 st = ln_stats<VEC>(ln_row, hidden, eps, scratch);
   T* o = out + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>((ln_row[i] - st.x) * st.y * gain[i]);
+  if (VEC) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x)
+      ln_store4(o + 4 * i, ln_apply(reinterpret_cast<const float4*>(ln_row)[i], st,
+                                    __ldg(reinterpret_cast<const float4*>(gain) + i)));
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>((ln_row[i] - st.x) * st.y * gain[i]);
+  }
 }
 
+#define LN_AHEAD 4
 template <typename T, bool VEC>
 __global__ void layernorm_into_residual_kernel(const float* y, const float* __restrict__ gain, float* x,
                                                const float* __restrict__ next_gain, T* next_out, int hidden, float eps,
                                                float next_eps, int accumulate) {
   extern __shared__ __align__(16) float ln_row[];
-  __shared__ float scratch[33];
+  __shared__ float scratch[128];
   pdl_trigger();
   pdl_wait();
   const size_t at = (size_t)blockIdx.x * hidden;
+  float* xr = x + at;
+  // the stream's row is asked for together with y's, so that one wait on memory covers both (rows of up to
+  // LN_AHEAD x 4 x blockDim numbers; longer ones read it where they need it)
+  float4 ahead[LN_AHEAD];
+  const bool early = VEC && accumulate && hidden / 4 <= LN_AHEAD * (int)blockDim.x;
+  if (early) {
+#pragma unroll
+    for (int k = 0; k < LN_AHEAD; k++) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < hidden / 4) ahead[k] = ld_fresh(reinterpret_cast<const float4*>(xr) + i);
+    }
+  }
   ln_load<VEC>(y + at, ln_row, hidden);
   __syncthreads();
-  const float2 st = ln_stats(ln_row, hidden, eps, scratch);
-  float* xr = x + at;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {      // a thread rewrites the entries it reads
-    float v = (ln_row[i] - st.x) * st.y * gain[i];
-    if (accumulate) v += ld_fresh(xr + i);
-    xr[i] = v;
-    ln_row[i] = v;
+  const float2 st = ln_stats<VEC>(ln_row, hidden, eps, scratch);
+  if (VEC && early) {                                            // a thread rewrites the entries it reads
+#pragma unroll
+    for (int k = 0; k < LN_AHEAD; k++) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < hidden / 4) {
+        float4 v = ln_apply(reinterpret_cast<const float4*>(ln_row)[i], st,
+                            __ldg(reinterpret_cast<const float4*>(gain) + i));
+        v.x += ahead[k].x; v.y += ahead[k].y; v.z += ahead[k].z; v.w += ahead[k].w;
+        reinterpret_cast<float4*>(xr)[i] = v;
+        reinterpret_cast<float4*>(ln_row)[i] = v;
+      }
+    }
+  } else if (VEC) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+      float4 v = ln_apply(reinterpret_cast<const float4*>(ln_row)[i], st,
+                          __ldg(reinterpret_cast<const float4*>(gain) + i));
+      if (accumulate) {
+        const float4 was = ld_fresh(reinterpret_cast<const float4*>(xr) + i);
+        v.x += was.x; v.y += was.y; v.z += was.z; v.w += was.w;
+      }
+      reinterpret_cast<float4*>(xr)[i] = v;
+      reinterpret_cast<float4*>(ln_row)[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = (ln_row[i] - st.x) * st.y * gain[i];
+      if (accumulate) v += ld_fresh(xr + i);
+      xr[i] = v;
+      ln_row[i] = v;
+    }
   }
   if (next_out == nullptr) return;
   __syncthreads();
-  const float2 nx = ln_stats(ln_row, hidden, next_eps, scratch);
+  const float2 nx = ln_stats<VEC>(ln_row, hidden, next_eps, scratch + 64);
   T* o = next_out + at;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    o[i] = from_float<T>((ln_row[i] - nx.x) * nx.y * next_gain[i]);
+  if (VEC) {
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x)
+      ln_store4(o + 4 * i, ln_apply(reinterpret_cast<const float4*>(ln_row)[i], nx,
+                                    __ldg(reinterpret_cast<const float4*>(next_gain) + i)));
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      o[i] = from_float<T>((ln_row[i] - nx.x) * nx.y * next_gain[i]);
+  }
 }
 
-static inline int ln_threads(int hidden) { return hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128); }
+// four vector loads a thread where the row allows it: more blocks an SM, at different points of their way
+static inline int ln_threads(int hidden) { return hidden > 4096 ? 512 : (hidden > 2048 ? 256 : 128); }
 
 template <typename KernelT>
 static int ln_shared(KernelT kernel, size_t bytes) {
@@ -95,7 +187,7 @@ template <typename T>
 static int launch_layernorm(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden,
                             float eps, cudaStream_t stream) {
   const size_t bytes = (size_t)hidden * sizeof(float);
-  const bool vec = hidden % 4 == 0 && (((uintptr_t)x) & 15) == 0;
+  const bool vec = hidden % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)gain) | ((uintptr_t)out)) & 15) == 0;
   auto kernel = vec ? layernorm_kernel<T, true> : layernorm_kernel<T, false>;
   const int bad = ln_shared(kernel, bytes);
   if (bad) return bad;
@@ -116,7 +208,8 @@ template <typename T>
 static int launch_into(const float* y, const float* gain, float* x, const float* next_gain, T* next_out, int n_rows,
                        int hidden, float eps, float next_eps, int accumulate, cudaStream_t stream) {
   const size_t bytes = (size_t)hidden * sizeof(float);
-  const bool vec = hidden % 4 == 0 && (((uintptr_t)y) & 15) == 0;
+  const bool vec = hidden % 4 == 0 &&
+                   ((((uintptr_t)y) | ((uintptr_t)gain) | ((uintptr_t)x) | ((uintptr_t)next_gain) | ((uintptr_t)next_out)) & 15) == 0;
   auto kernel = vec ? layernorm_into_residual_kernel<T, true> : layernorm_into_residual_kernel<T, false>;
   const int bad = ln_shared(kernel, bytes);
   if (bad) return bad;
