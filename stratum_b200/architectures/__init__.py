@@ -1,1 +1,1 @@
-from . import dabodra, llama, nibelorn, vitinex  # noqa: F401  (registers the architectures)
+from . import dabodra, llama, mokatar, nibelorn, vitinex  # noqa: F401  (registers the architectures)

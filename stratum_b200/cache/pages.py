@@ -120,13 +120,16 @@ class SequencePages:
 
     `window` = 0 keeps every key; `window` = W keeps only what the next query can
     still see (the last W positions), so pages that fall wholly behind the window
-    go back to the pool as the sequence grows.  Entry i of `table` is the page
-    that holds positions [i*PAGE_TOKENS, (i+1)*PAGE_TOKENS), or -1 once dropped.
+    go back to the pool as the sequence grows; with `keep_first` = F the pages that
+    hold any of the first F positions stay as well (a window that never loses the
+    sequence's first tokens).  Entry i of `table` is the page that holds positions
+    [i*PAGE_TOKENS, (i+1)*PAGE_TOKENS), or -1 once dropped.
     """
 
-    def __init__(self, pool: PagePool, window: int = 0):
+    def __init__(self, pool: PagePool, window: int = 0, keep_first: int = 0):
         self.pool = pool
         self.window = window
+        self.keep_first = keep_first
         self.table: List[int] = []
         self.length = 0
 
@@ -144,10 +147,11 @@ class SequencePages:
             raise CacheMisuse("sequence advanced beyond its reserved pages")
         if self.window > 0:
             first_needed = max(0, self.length - self.window + 1) // PAGE_TOKENS
-            drop = [p for p in self.table[:first_needed] if p >= 0]
+            kept = pages_for(self.keep_first)
+            drop = [p for p in self.table[kept:first_needed] if p >= 0]
             if drop:
                 self.pool.give(drop)
-                for i in range(first_needed):
+                for i in range(kept, first_needed):
                     self.table[i] = -1
                 return True
         return False

@@ -36,6 +36,8 @@ class KVSpec:
     # keys); value_heads = 0: no values are stored (a mixer whose values are a stretch of its key rows)
     value_heads: Optional[int] = None
     value_dim: Optional[int] = None
+    # with a window: the first `keep_first` positions of a sequence stay visible (and held) whatever its length
+    keep_first: int = 0
 
     @property
     def v_heads(self) -> int:
@@ -48,7 +50,7 @@ class KVSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """A fixed-size block per sequence, zeroed when a slot is taken.  dtype: "float32" or "compute"."""
+    """A fixed-size block per sequence, zeroed when a slot is taken.  dtype: "float32", "int32" or "compute"."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
 
@@ -124,7 +126,7 @@ class SequenceCache:
                     shape_v = (n, self.n_pages, g.spec.v_heads, PAGE_TOKENS, g.spec.v_dim)
                     g.v = torch.zeros(shape_v, dtype=self.dtype, device=self.device)
             else:
-                dt = torch.float32 if g.spec.dtype == "float32" else self.dtype
+                dt = {"float32": torch.float32, "int32": torch.int32}.get(g.spec.dtype, self.dtype)
                 # one row more than there are slots: row `max_seqs` belongs to no sequence; the padding rows of a
                 # step point there, so a mixer may update "their" state without harm to anyone's
                 g.state = torch.zeros((n, self.max_seqs + 1) + tuple(g.spec.shape), dtype=dt, device=self.device)
@@ -140,7 +142,7 @@ class SequenceCache:
     # ------------------------------------------------------------------ sequences
     def acquire(self) -> int:
         slot = self.slots.acquire()
-        self._seq[slot] = [SequencePages(g.pool, g.spec.window) if isinstance(g.spec, KVSpec) else None
+        self._seq[slot] = [SequencePages(g.pool, g.spec.window, g.spec.keep_first) if isinstance(g.spec, KVSpec) else None
                            for g in self.groups]
         for g in self.groups:
             if g.state is not None:

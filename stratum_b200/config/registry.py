@@ -7,7 +7,7 @@ architecture names and lists the known ones when a name is not found
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Tuple, Type
+from typing import Any, Callable, Dict, List, Optional, Tuple, Type
 
 from .base import ConfigError, ModelConfig
 
@@ -21,6 +21,9 @@ class Architecture:
     # tensors a published file may carry that the model does not use (buffers, not weights): names ending in one
     # of these are left alone by the loader instead of being reported as unexpected
     ignored_tensor_suffixes: Tuple[str, ...] = ()
+    # (config, {tensor name: shape}) -> config: for a design whose config.json leaves a size to the shape of a
+    # tensor; called with the shapes a model folder (or a set of tensors in memory) holds before the model is described
+    sizes_from_tensors: Optional[Callable[[ModelConfig, Dict[str, Tuple[int, ...]]], ModelConfig]] = None
 
 
 _ARCHITECTURES: List[Architecture] = []

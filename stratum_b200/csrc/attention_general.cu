@@ -9,7 +9,8 @@
 //   key head   kh = (h / group) * maps + m          value head  vh = h / group
 //   score_t    = (q[h][m] . K_t[kh]) * scale * temp(p),  temp(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)
 //   score_t   <- softcap * tanh(score_t / softcap)       (softcap > 0)
-//   a_m        = sum_t softmax_t(score) V_t[vh]           over the keys t in [lo, p], lo = 0 or p - window + 1
+//   a_m        = sum_t softmax_t(score) V_t[vh]           over the keys t in [lo, p], lo = 0 or p - window + 1,
+//                                                         and with a window also the keys t < keep_first
 // Values: rows of the value cache, or (v_in_k) the first v_dim values of the key rows of head (h / group) * maps.
 // sink: where given, exp(sink[h]) is one more term of every softmax's denominator (it has no key and no value).
 // combine 0 (maps = 1): out[h] = a_0.
@@ -47,6 +48,9 @@ attention_general_kernel(const GeneralAttention P) {
   if (P.temp_coef != 0.f) temp = 1.f + P.temp_coef * logf((float)((pos + 1) / P.temp_every) + 1.f);
   const float factor = P.scale * temp;
   const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+  // chunks are visited in key order: those that hold kept first keys, then those from the window's first key on
+  const int first_win = (lo / 32) * 32;
+  const int kept_end = min(P.window > 0 ? P.keep_first : 0, lo);
   const int* bt = P.block_table + (size_t)seq * P.bt_stride;
   const int kv = h / P.group;
   const size_t k_page = (size_t)P.n_k_heads * P.page_tokens * D;
@@ -64,9 +68,13 @@ attention_general_kernel(const GeneralAttention P) {
     for (int i = 0; i < VCH; i++) acc[m][i] = 0.f;
   }
 
-  for (int base = (lo / 32) * 32; base <= pos; base += 32) {
+  for (int base = 0; base <= pos; base += 32) {
+    if (base >= kept_end && base < first_win) {      // nothing between the kept keys and the window is seen
+      base = first_win - 32;
+      continue;
+    }
     const int key = base + lane;
-    const bool valid = key >= lo && key <= pos;
+    const bool valid = (key >= lo || key < kept_end) && key <= pos;
     const int page = bt[base / P.page_tokens];      // page_tokens is a multiple of 32: one page per chunk
     const int in_page = base % P.page_tokens;
     const T* vr = vbase + (size_t)page * v_page + v_head + (size_t)in_page * v_row;

@@ -23,7 +23,8 @@ struct GeneralAttention {
   int qk_dim, v_dim, n_k_heads, n_v_heads, v_in_k;
   int page_tokens, window, combine, gate_col;
   int temp_every, n_qblocks, tokens_per_block, n_splits, chunk, reserved;
-  int dense, ldk, ldv, reserved2;   // dense: keys and values are rows of plain matrices (see attention_general_mma.cu)
+  int dense, ldk, ldv;      // dense: keys and values are rows of plain matrices (see attention_general_mma.cu)
+  int keep_first;           // with a window: keys at positions below this stay visible to every later row
   float scale, softcap, temp_coef, lambda, out_scale, eps;
 };
 
@@ -34,6 +35,7 @@ static inline int general_attention_check(const GeneralAttention& P) {
   if (P.v_in_k ? P.v_dim > P.qk_dim : P.n_v_heads != P.n_heads / P.group) return STRATUM_ERR_SHAPE;
   if (P.combine == 0 ? P.maps != 1 : (P.combine != 1 || P.maps != 2)) return STRATUM_ERR_SHAPE;
   if (P.temp_coef != 0.f && P.temp_every < 1) return STRATUM_ERR_SHAPE;
+  if (P.window < 0 || P.keep_first < 0) return STRATUM_ERR_SHAPE;
   if (P.ldq < P.n_heads * P.maps * P.qk_dim || P.ldo < P.n_heads * P.v_dim) return STRATUM_ERR_SHAPE;
   return 0;
 }

@@ -109,9 +109,12 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const int first_pos = P.token_pos[tok0];
   const int last_pos = first_pos + ntok - 1;
   const int lo_block = (P.window > 0 && first_pos - P.window + 1 > 0) ? first_pos - P.window + 1 : 0;
-  int k_begin = split * P.chunk;
+  const int k_begin = split * P.chunk;
   const int k_end = min((split + 1) * P.chunk, last_pos + 1);
-  if (k_begin < (lo_block / GM_TILE) * GM_TILE) k_begin = (lo_block / GM_TILE) * GM_TILE;
+  // tiles wholly in front of the window of the block's first row hold nothing any row sees, unless they hold kept
+  // first keys (positions below keep_first stay visible through a window)
+  const int lo_tile = (lo_block / GM_TILE) * GM_TILE;
+  const int keep = P.window > 0 ? P.keep_first : 0;
   const bool dense = P.dense != 0;
   const int* bt = dense ? nullptr : P.block_table + (size_t)seq * P.bt_stride;
   const size_t seq_row0 = dense ? (size_t)P.seq_start[seq] : 0;
@@ -156,6 +159,10 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
   for (int key0 = (k_begin / GM_TILE) * GM_TILE; key0 < k_end; key0 += GM_TILE) {
+    if (key0 < lo_tile && key0 >= keep) {          // on to the window's first tile (the same for every thread)
+      key0 = lo_tile - GM_TILE;
+      continue;
+    }
     const int kw = key0 + 16 * warp;
     const bf16* kr;
     const bf16* vr;
@@ -220,7 +227,7 @@ attention_general_mma_kernel(const GeneralAttention P) {
             const int key = kw + 8 * i + 2 * t + (j & 1);
             const int pos = row_pos[rg][e];
             const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
-            const bool ok = any && row_ok[rg][e] && key <= pos && key >= lo && key < k_end && key >= k_begin;
+            const bool ok = any && row_ok[rg][e] && key <= pos && (key >= lo || key < keep) && key < k_end && key >= k_begin;
             v = ok ? v : -INFINITY;
           }
           s[rg][i][j] = v;

@@ -27,7 +27,7 @@ NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompi
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
            "gemm_tc", "attention_tc", "attention_stream", "attention_static", "attention_general", "attention_general_mma",
-           "mixer_prep", "head_gemm", "sublayer_norm", "qk_norm_rope", "delta_rule", "moe_router", "layer_norm", "ssm_scan")
+           "mixer_prep", "head_gemm", "sublayer_norm", "qk_norm_rope", "delta_rule", "moe_router", "layer_norm", "ssm_scan", "gla")
 HEADERS = ("common.cuh",)
 EXTRA_DEPS = {"attention_general": ("attention_general.h",),
               "attention_general_mma": ("attention_general.h", "mma_common.cuh"), "head_gemm": ("mma_common.cuh",),

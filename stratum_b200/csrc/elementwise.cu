@@ -34,6 +34,95 @@ STRATUM_EXPORT int stratum_embed_gather(const void* table, int dtype, const int*
   return STRATUM_ERR_DTYPE;
 }
 
+// ---------------------------------------------------------------- embedding with a table of token pairs
+// out[t] = table[ids[t]] * scale + pairs[row(t)], float32, where row(t) = (prev * mul_prev + id * mul_cur) mod buckets
+// with prev the token in front of t in its sequence, and row(t) = buckets (the table's last row) for a sequence's
+// first token.  The token in front of a step's first token is what the step before left in `last` (one int per
+// cache slot); the thread that reads it then stores the sequence's last token of this step there, so the entry is
+// read before it is rewritten.  Tokens of no sequence (sequence index -1) read row `buckets` and touch no state.
+// out2, where given, receives the same rows (a model that adds the embedded tokens to its stream again later).
+struct EmbedPairs {
+  const void* table;        // [vocab][hidden]
+  const void* pairs;        // [buckets + 1][hidden]
+  const int* ids;
+  const int* token_pos;
+  const int* token_seq;
+  const int* seq_start;     // [seqs + 1]
+  const int* seq_slot;      // [seqs]
+  int* last;                // [slots]
+  float* out;
+  float* out2;
+  int n_tokens, hidden, vocab, buckets;
+  int mul_prev, mul_cur, write_state, reserved;
+  float scale, reserved2;
+};
+
+template <typename T>
+__global__ void embed_pairs_kernel(const EmbedPairs P) {
+  __shared__ int row_s;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = P.ids[t];
+  if (id < 0 || id >= P.vocab) id = 0;
+  if (threadIdx.x == 0) {
+    const int seq = P.token_seq[t];
+    int prev = -1;
+    if (seq >= 0) {
+      const int start = P.seq_start[seq], slot = P.seq_slot[seq];
+      if (t > start) prev = P.ids[t - 1];
+      else if (P.token_pos[t] > 0) prev = __ldcg(P.last + slot);
+      if (t == start && P.write_state) P.last[slot] = P.ids[P.seq_start[seq + 1] - 1];
+    }
+    if (prev >= P.vocab) prev = 0;
+    row_s = prev < 0 ? P.buckets
+                     : (int)(((long long)prev * P.mul_prev + (long long)id * P.mul_cur) % (long long)P.buckets);
+  }
+  __syncthreads();
+  const T* a = (const T*)P.table + (size_t)id * P.hidden;
+  const T* b = (const T*)P.pairs + (size_t)row_s * P.hidden;
+  float* o = P.out + (size_t)t * P.hidden;
+  float* o2 = P.out2 ? P.out2 + (size_t)t * P.hidden : nullptr;
+  for (int i = threadIdx.x; i < P.hidden; i += blockDim.x) {
+    const float v = fmaf(to_float(a[i]), P.scale, to_float(b[i]));
+    o[i] = v;
+    if (o2) o2[i] = v;
+  }
+}
+
+STRATUM_EXPORT int stratum_embed_pairs(const EmbedPairs* params, int dtype, cudaStream_t stream) {
+  const EmbedPairs& P = *params;
+  if (P.n_tokens <= 0) return 0;
+  if (P.buckets < 1 || P.hidden < 1 || P.vocab < 1 || P.mul_prev < 0 || P.mul_cur < 0) return STRATUM_ERR_SHAPE;
+  const int threads = P.hidden >= 1024 ? 256 : 128;
+  if (dtype == STRATUM_DT_F32) launch_pdl(embed_pairs_kernel<float>, P.n_tokens, threads, 0, stream, P);
+  else if (dtype == STRATUM_DT_BF16) launch_pdl(embed_pairs_kernel<bf16>, P.n_tokens, threads, 0, stream, P);
+  else return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
+
+// x[t] += a[t] (where given) + row, all float32 [tokens][hidden] / [hidden]: the head of a pass over looped layers
+// that takes the embedded tokens in again and adds the pass's own vector.
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ row,
+                                size_t n, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = ld_fresh(x + i);
+    if (a) v += ld_fresh(a + i);
+    x[i] = v + row[i % hidden];
+  }
+}
+
+STRATUM_EXPORT int stratum_add_rows(float* x, const float* a, const float* row, int n_tokens, int hidden,
+                                    cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const size_t n = (size_t)n_tokens * hidden;
+  const size_t blocks = (n + 255) / 256;
+  return launch_pdl(add_rows_kernel, (unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, stream, x, a, row, n,
+                    hidden);
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // y = x * (1/sqrt(mean(x^2) + eps)) * gain     (stratum/native/stratum_arch_llama.inc.c:45-76)
 // x float32 [*, hidden]; row r of the output reads row rows[r] of x when rows != nullptr

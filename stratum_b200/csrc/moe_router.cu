@@ -10,7 +10,8 @@
 //   Variants, all parameters: score = 1 takes s = softmax(z) over all experts in sigmoid's place; renorm = 0 leaves
 //   the chosen scores as they are (weight s_e * scale); correction may be absent; with w_gate (one more row of
 //   `width` weights) the token's sigmoid(w_gate . h) is written behind the experts' weights, dense[t][n_experts]:
-//   the gate of a shared expert.
+//   the gate of a shared expert; with `bias` the logits are z = W_r h + bias.  (Softmax scores divided by the sum of
+//   the chosen ones are the softmax over the chosen logits alone.)
 // scale_column_blocks: a[t][e * block + j] *= w[t][e] for e < n_blocks (columns beyond n_blocks * block are left
 //   alone): the activations of every expert, side by side in one row, times the token's weight for that expert, so
 //   that one product with the experts' stacked down matrices sums the weighted expert outputs.
@@ -34,6 +35,7 @@ struct MoeRoute {
   float scale, reserved;
   const float* w_gate;      // [width] or null
   int score, renorm;        // score: 0 sigmoid, 1 softmax over all experts;  renorm: weights divided by their sum
+  const float* bias;        // [n_experts] or null: added to the logits z before anything else
 };
 
 #define MR_WARPS 8
@@ -97,6 +99,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
       for (int i = lane; i < P.width; i += 32) acc = fmaf(ld_fresh(x + i), w[i], acc);
     }
     acc = warp_sum(acc);
+    if (P.bias && e < E) acc += P.bias[e];
     if (lane == 0) {
       const float sg = 1.0f / (1.0f + expf(-acc));
       if (e == E) {

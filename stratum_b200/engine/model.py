@@ -19,7 +19,7 @@ from ..config.registry import find_architecture
 from ..parts import find_part
 from ..parts.base import Runtime
 from ..parts.spec import LayerSpec, ModelSpec, TensorSpec
-from ..weights.loader import check_tensors, load_weights, place
+from ..weights.loader import check_tensors, load_weights, place, tensor_shapes
 
 
 class Layer:
@@ -94,7 +94,7 @@ class Model:
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
         """Per stop of the schedule: what its mixer keeps per sequence (None if nothing, or if the stop
-        reads another stop's cache)."""
+        reads another stop's cache); then, if the embedding keeps anything per sequence, one more entry for it."""
         specs: List[Optional[CacheSpec]] = []
         for i, e in enumerate(self.schedule):
             own = self.layers[e.layer].cache_spec()
@@ -105,6 +105,8 @@ class Model:
                                      f"which holds {theirs}")
                 own = None
             specs.append(own)
+        if self.embedding.cache_spec() is not None:      # one more owner behind the stops: the embedding's state
+            specs.append(self.embedding.cache_spec())
         return specs
 
     # ------------------------------------------------------------------ weights
@@ -127,12 +129,11 @@ class Model:
     # ------------------------------------------------------------------ forward
     def forward(self, step, cache) -> torch.Tensor:
         """Run the tokens of one step through every stop of the schedule; float32 logits at the wanted rows."""
-        x = self.embedding.forward(step.token_ids)
+        x = self.embedding.forward_step(step, cache.layer_view(len(self.schedule), True, step.block_tables),
+                                        keep=self.spec.keep_embedded)
         if self.position is not None:
             self.position.add_to_embedding(x, step)
-        if self.spec.keep_embedded:       # a second gather, not a copy: the stream itself is rewritten in place
-            step.embedded = self.embedding.forward(step.token_ids)
-            if self.position is not None:
+            if self.spec.keep_embedded:
                 self.position.add_to_embedding(step.embedded, step)
         carry = None                  # rows a layer's last product prepared for the next layer's first norm
         for stop, entry in enumerate(self.schedule):
@@ -169,6 +170,8 @@ def expected_tensors(config: ModelConfig) -> Dict[str, TensorSpec]:
 def load_model(model_dir: str, dtype: torch.dtype, device="cuda") -> Tuple[Model, ModelConfig]:
     """config.json picks the architecture; weights are bound by name."""
     config, arch = config_from_dir(model_dir)
+    if arch.sizes_from_tensors is not None:
+        config = arch.sizes_from_tensors(config, tensor_shapes(model_dir))
     runtime = Runtime(dtype, device)
     model = Model(arch.describe_model(config), runtime)
     weights = load_weights(model_dir, model.tensors(), dtype, runtime.device, arch.ignored_tensor_suffixes)
@@ -180,6 +183,8 @@ def model_from_tensors(config: ModelConfig, tensors: Mapping[str, torch.Tensor],
                        device="cuda") -> Model:
     """Build from tensors already in memory (checked like a file's)."""
     arch = find_architecture(config.architecture)
+    if arch.sizes_from_tensors is not None:
+        config = arch.sizes_from_tensors(config, {n: tuple(t.shape) for n, t in tensors.items()})
     runtime = Runtime(dtype, device)
     model = Model(arch.describe_model(config), runtime)
     expected = model.tensors()

@@ -151,6 +151,58 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> N
              table.shape[0], _stream()), "embed_gather")
 
 
+class _EmbedPairs(ctypes.Structure):
+    """Mirror of struct EmbedPairs in csrc/elementwise.cu."""
+    _fields_ = [("table", c_void_p), ("pairs", c_void_p), ("ids", c_void_p), ("token_pos", c_void_p),
+                ("token_seq", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("last", c_void_p),
+                ("out", c_void_p), ("out2", c_void_p),
+                ("n_tokens", c_int), ("hidden", c_int), ("vocab", c_int), ("buckets", c_int),
+                ("mul_prev", c_int), ("mul_cur", c_int), ("write_state", c_int), ("reserved", c_int),
+                ("scale", c_float), ("reserved2", c_float)]
+
+
+def embed_pairs(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, token_pos: torch.Tensor,
+                token_seq: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, last: torch.Tensor,
+                out: torch.Tensor, out2: Optional[torch.Tensor], scale: float, mul_prev: int, mul_cur: int,
+                write_state: bool = True) -> None:
+    """out[t] = table[ids[t]] * scale + pairs[(prev * mul_prev + ids[t] * mul_cur) mod buckets], float32; prev is the
+    token in front of t in its sequence (from the step, or from `last`, int32 [slots, 1], which then takes the
+    sequence's last token of this step); a sequence's first token reads the last row of pairs [buckets + 1, hidden].
+    out2 (or None) receives the same rows."""
+    _need(table, "table"); _need(pairs, "pairs", table.dtype); _need(ids, "ids", torch.int32)
+    _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
+    _need(seq_start, "seq_start", torch.int32); _need(seq_slot, "seq_slot", torch.int32)
+    _need(last, "last", torch.int32); _need(out, "out", torch.float32)
+    if pairs.shape[1] != table.shape[1] or out.shape != (ids.numel(), table.shape[1]) or pairs.shape[0] < 2:
+        raise KernelError("embed_pairs: shapes disagree")
+    p = _EmbedPairs()
+    p.table, p.pairs, p.ids, p.token_pos = table.data_ptr(), pairs.data_ptr(), ids.data_ptr(), token_pos.data_ptr()
+    p.token_seq, p.seq_start, p.seq_slot = token_seq.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr()
+    p.last, p.out = last.data_ptr(), out.data_ptr()
+    if out2 is not None:
+        _need(out2, "out2", torch.float32)
+        if out2.shape != out.shape:
+            raise KernelError("embed_pairs: out2 and out disagree")
+        p.out2 = out2.data_ptr()
+    p.n_tokens, p.hidden, p.vocab, p.buckets = ids.numel(), table.shape[1], table.shape[0], pairs.shape[0] - 1
+    p.mul_prev, p.mul_cur, p.write_state, p.scale = int(mul_prev), int(mul_cur), int(bool(write_state)), float(scale)
+    f = _fn("elementwise", "stratum_embed_pairs", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(table.dtype), _stream()), "embed_pairs")
+
+
+def add_rows(x: torch.Tensor, a: Optional[torch.Tensor], row: torch.Tensor) -> None:
+    """x[t] += a[t] (where given) + row: x, a float32 [tokens, hidden], row float32 [hidden]."""
+    _need(x, "x", torch.float32); _need(row, "row", torch.float32)
+    if a is not None:
+        _need(a, "a", torch.float32)
+        if a.shape != x.shape:
+            raise KernelError("add_rows: a and x disagree")
+    if row.numel() != x.shape[1]:
+        raise KernelError("add_rows: row and x disagree")
+    f = _fn("elementwise", "stratum_add_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(a), _ptr(row), x.shape[0], x.shape[1], _stream()), "add_rows")
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(x[rows[r]] or x[r]) * gain.  x float32 [*,H], gain float32 [H]."""
@@ -616,7 +668,7 @@ class _GeneralAttention(ctypes.Structure):
                 ("page_tokens", c_int), ("window", c_int), ("combine", c_int), ("gate_col", c_int),
                 ("temp_every", c_int), ("n_qblocks", c_int), ("tokens_per_block", c_int), ("n_splits", c_int),
                 ("chunk", c_int), ("reserved", c_int),
-                ("dense", c_int), ("ldk", c_int), ("ldv", c_int), ("reserved2", c_int),
+                ("dense", c_int), ("ldk", c_int), ("ldv", c_int), ("keep_first", c_int),
                 ("scale", c_float), ("softcap", c_float), ("temp_coef", c_float), ("lam", c_float),
                 ("out_scale", c_float), ("eps", c_float)]
 
@@ -624,14 +676,16 @@ class _GeneralAttention(ctypes.Structure):
 class AttentionShape:
     """The constants of a general attention (see csrc/attention_general.cu): heads, query heads per key/value
     head (`group`), score maps per head, key and value sizes, whether the values are the first v_dim values of
-    the key rows, scale, softcap (0: none), window (0: every key), the query factor
+    the key rows, scale, softcap (0: none), window (0: every key; keep_first: with a window, the positions below it stay
+    visible), the query factor
     1 + temp_coef ln(floor((p + 1) / temp_every) + 1), and for two maps the combination
     (a_0 - lam a_1) / rms * out_scale with its eps and the column of the output gate (-1: none)."""
 
     def __init__(self, n_heads: int, group: int, maps: int, qk_dim: int, v_dim: int, v_in_k: bool, scale: float,
                  softcap: float = 0.0, window: int = 0, temp_coef: float = 0.0, temp_every: int = 1,
                  lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0, gate_col: int = -1,
-                 sink: Optional[torch.Tensor] = None):
+                 sink: Optional[torch.Tensor] = None, keep_first: int = 0):
+        self.keep_first = int(keep_first) if window > 0 else 0
         self.n_heads, self.group, self.maps, self.qk_dim, self.v_dim = n_heads, group, maps, qk_dim, v_dim
         self.v_in_k, self.scale, self.softcap, self.window = bool(v_in_k), scale, softcap, window
         self.temp_coef, self.temp_every, self.lam, self.out_scale = temp_coef, temp_every, lam, out_scale
@@ -648,7 +702,7 @@ class AttentionShape:
         p.n_v_heads = 0 if self.v_in_k else self.n_heads // self.group
         p.v_in_k, p.window, p.combine, p.gate_col = int(self.v_in_k), self.window, int(self.maps == 2), self.gate_col
         p.temp_every, p.scale, p.softcap, p.temp_coef = self.temp_every, self.scale, self.softcap, self.temp_coef
-        p.lam, p.out_scale, p.eps = self.lam, self.out_scale, self.eps
+        p.lam, p.out_scale, p.eps, p.keep_first = self.lam, self.out_scale, self.eps, self.keep_first
         p.sink = None if self.sink is None else self.sink.data_ptr()
 
 
@@ -825,22 +879,29 @@ class _QKNormRope(ctypes.Structure):
                 ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("ld", c_int), ("ldq", c_int), ("bt_stride", c_int), ("n_tokens", c_int),
                 ("n_heads", c_int), ("n_kv", c_int), ("dim", c_int), ("rot_pairs", c_int),
-                ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float), ("reserved", c_float)]
+                ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float), ("magnitude", c_float),
+                ("v_dim", c_int), ("per_head", c_int), ("half", c_int), ("reserved", c_int)]
 
 
 def qk_norm_rope(proj: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
                  q_gain: torch.Tensor, k_gain: torch.Tensor, inv_freq: Optional[torch.Tensor], eps: float,
                  q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int, n_kv: int,
-                 dim: int, page_tokens: int, write_cache: bool) -> None:
-    """proj float32 [tokens, >= (n_heads + n_kv) * dim] holds queries then keys as projected.  The key columns go,
-    as they are, to v_cache; queries and keys are divided by the root mean square of their whole stretch (eps inside
-    the root) times a gain per column, the first 2 * len(inv_freq) dimensions of every head are rotated (pairs
-    (2i, 2i + 1), angle position * inv_freq[i]); queries go to q_out [tokens, >= n_heads * dim], keys to k_cache
-    (caches [pages, n_kv, page_tokens, dim], of q_out's dtype)."""
+                 dim: int, page_tokens: int, write_cache: bool, v_dim: int = 0, per_head: bool = False,
+                 half: bool = False, magnitude: float = 1.0) -> None:
+    """proj float32 [tokens, >= (n_heads + n_kv) * dim + n_kv * v_dim] holds queries, keys and (v_dim > 0) values as
+    projected.  v_dim = 0: the key columns go, as they are, to v_cache; else the value columns do (v_cache [pages,
+    n_kv, page_tokens, v_dim]).  Queries and keys are divided by a root mean square (eps inside the root) and
+    multiplied by a gain: of their whole stretch with a gain per column, or (per_head) of each head with one gain of
+    `dim` values for all heads; the first 2 * len(inv_freq) dimensions of every head are rotated by position *
+    inv_freq[i], pairs (2i, 2i + 1) or (half) (i, i + len(inv_freq)), cos and sin times `magnitude`; queries go to
+    q_out [tokens, >= n_heads * dim], keys to k_cache [pages, n_kv, page_tokens, dim] (of q_out's dtype)."""
     _need(proj, "proj", torch.float32, contiguous=False); _need(token_pos, "token_pos", torch.int32)
     _need(token_seq, "token_seq", torch.int32); _need(q_gain, "q_gain", torch.float32)
     _need(k_gain, "k_gain", torch.float32); _need(q_out, "q_out", contiguous=False)
-    if q_gain.numel() != n_heads * dim or k_gain.numel() != n_kv * dim:
+    if per_head:
+        if q_gain.numel() != dim or k_gain.numel() != dim:
+            raise KernelError("qk_norm_rope: one gain per dimension of a head")
+    elif q_gain.numel() != n_heads * dim or k_gain.numel() != n_kv * dim:
         raise KernelError("qk_norm_rope: one gain per projected column")
     p = _QKNormRope()
     p.proj, p.token_pos, p.token_seq = proj.data_ptr(), token_pos.data_ptr(), token_seq.data_ptr()
@@ -850,10 +911,13 @@ def qk_norm_rope(proj: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.T
         p.inv_freq, p.rot_pairs = inv_freq.data_ptr(), inv_freq.numel()
     p.ld, p.ldq, p.n_tokens = proj.stride(0), q_out.stride(0), proj.shape[0]
     p.n_heads, p.n_kv, p.dim, p.page_tokens, p.eps = n_heads, n_kv, dim, page_tokens, float(eps)
+    p.v_dim, p.per_head, p.half, p.magnitude = int(v_dim), int(bool(per_head)), int(bool(half)), float(magnitude)
     p.write_cache = int(bool(write_cache))
     if write_cache:
         _need(block_table, "block_table", torch.int32, contiguous=False)
         _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype)
+        if k_cache.shape[-1] != dim or v_cache.shape[-1] != (v_dim or dim):
+            raise KernelError("qk_norm_rope: the caches' rows and the head sizes disagree")
         p.block_table, p.bt_stride = block_table.data_ptr(), block_table.stride(0)
         p.k_cache, p.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
     f = _fn("qk_norm_rope", "stratum_qk_norm_rope", [c_void_p, c_int, c_void_p])
@@ -959,6 +1023,50 @@ def ssm_scan(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, a_l
     count_launches(2)
 
 
+# ------------------------------------------------------------------ gated linear attention
+class _Gla(ctypes.Structure):
+    """Mirror of struct Gla in csrc/gla.cu."""
+    _fields_ = [("proj", c_void_p), ("w_a2", c_void_p), ("b_a2", c_void_p), ("gain", c_void_p), ("alpha", c_void_p),
+                ("o_raw", c_void_p), ("out", c_void_p), ("state", c_void_p), ("token_seq", c_void_p),
+                ("seq_start", c_void_p), ("seq_slot", c_void_p),
+                ("ld", c_int), ("ldo", c_int), ("n_tokens", c_int), ("n_seqs", c_int),
+                ("n_heads", c_int), ("dim", c_int), ("vdim", c_int), ("rank", c_int),
+                ("state_stride", c_int), ("write_state", c_int),
+                ("eps", c_float), ("inv_tau", c_float), ("q_scale", c_float), ("reserved", c_float)]
+
+
+def gla(proj: torch.Tensor, w_a2: torch.Tensor, b_a2: torch.Tensor, gain: torch.Tensor, alpha: torch.Tensor,
+        o_raw: torch.Tensor, out: torch.Tensor, state: torch.Tensor, token_seq: torch.Tensor, seq_start: torch.Tensor,
+        seq_slot: torch.Tensor, n_heads: int, dim: int, vdim: int, tau: float, q_scale: float, eps: float,
+        write_state: bool = True) -> None:
+    """Gated linear attention over a step (see csrc/gla.cu): proj float32 [tokens, >= 2 heads dim + 2 heads vdim +
+    rank] holds q | k | v | g | the decay's inner projection; w_a2 [heads * dim, rank] in out's dtype, b_a2 float32;
+    alpha float32 [tokens, heads * dim] and o_raw float32 [tokens, heads * vdim] are scratch; state float32 [slots,
+    >= heads * vdim * dim] holds every sequence's S^T; out [tokens, >= heads * vdim] receives the normed, gated
+    read-out in the compute dtype."""
+    _need(proj, "proj", torch.float32, contiguous=False); _need(w_a2, "w_a2", out.dtype)
+    _need(b_a2, "b_a2", torch.float32); _need(gain, "gain", torch.float32); _need(alpha, "alpha", torch.float32)
+    _need(o_raw, "o_raw", torch.float32); _need(out, "out", contiguous=False); _need(state, "state", torch.float32)
+    _need(token_seq, "token_seq", torch.int32); _need(seq_start, "seq_start", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    T = proj.shape[0]
+    if (w_a2.shape[0] != n_heads * dim or b_a2.numel() != n_heads * dim or gain.numel() != vdim
+            or alpha.shape != (T, n_heads * dim) or o_raw.shape != (T, n_heads * vdim) or out.shape[0] != T
+            or state.dim() != 2):
+        raise KernelError("gla: shapes disagree")
+    p = _Gla()
+    p.proj, p.w_a2, p.b_a2, p.gain = proj.data_ptr(), w_a2.data_ptr(), b_a2.data_ptr(), gain.data_ptr()
+    p.alpha, p.o_raw, p.out, p.state = alpha.data_ptr(), o_raw.data_ptr(), out.data_ptr(), state.data_ptr()
+    p.token_seq, p.seq_start, p.seq_slot = token_seq.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr()
+    p.ld, p.ldo, p.n_tokens, p.n_seqs = proj.stride(0), out.stride(0), T, seq_slot.numel()
+    p.n_heads, p.dim, p.vdim, p.rank = n_heads, dim, vdim, w_a2.shape[1]
+    p.state_stride, p.write_state = state.stride(0), int(bool(write_state))
+    p.eps, p.inv_tau, p.q_scale = float(eps), 1.0 / float(tau), float(q_scale)
+    f = _fn("gla", "stratum_gla", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(out.dtype), _stream()), "gla")
+    count_launches(2)          # prep, recurrence and finish are three launches
+
+
 # ------------------------------------------------------------------ routed experts
 class _MoeRoute(ctypes.Structure):
     """Mirror of struct MoeRoute in csrc/moe_router.cu."""
@@ -966,17 +1074,20 @@ class _MoeRoute(ctypes.Structure):
                 ("chosen", c_void_p), ("weights", c_void_p),
                 ("ldx", c_int), ("ldd", c_int), ("n_tokens", c_int), ("width", c_int),
                 ("n_experts", c_int), ("top", c_int), ("n_groups", c_int), ("keep", c_int),
-                ("scale", c_float), ("reserved", c_float), ("w_gate", c_void_p), ("score", c_int), ("renorm", c_int)]
+                ("scale", c_float), ("reserved", c_float), ("w_gate", c_void_p), ("score", c_int), ("renorm", c_int),
+                ("bias", c_void_p)]
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], dense: torch.Tensor,
               chosen: torch.Tensor, weights: torch.Tensor, top: int, n_groups: int, keep: int, scale: float,
-              softmax: bool = False, renorm: bool = True, w_gate: Optional[torch.Tensor] = None) -> None:
+              softmax: bool = False, renorm: bool = True, w_gate: Optional[torch.Tensor] = None,
+              bias: Optional[torch.Tensor] = None) -> None:
     """Routing with a choice correction and groups (see csrc/moe_router.cu): scores by sigmoid, or by softmax over all
     experts; the chosen scores divided by their sum (renorm) or left as they are.  x [tokens, width] float32 or
     bfloat16; w_router float32 [experts, width]; correction float32 [experts] or None; dense float32 [tokens, >=
     experts] (weights, zeros for experts not chosen); chosen int32 and weights float32 [tokens, top].  w_gate
-    float32 [width]: dense[:, experts] receives sigmoid(x . w_gate), the gate of a shared expert."""
+    float32 [width]: dense[:, experts] receives sigmoid(x . w_gate), the gate of a shared expert.  bias float32
+    [experts]: added to the router's products before they are scored."""
     _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32)
     _need(dense, "dense", torch.float32, contiguous=False)
     _need(chosen, "chosen", torch.int32); _need(weights, "weights", torch.float32)
@@ -989,6 +1100,11 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     p = _MoeRoute()
     p.x, p.w_router, p.correction = x.data_ptr(), w_router.data_ptr(), (0 if correction is None else correction.data_ptr())
     p.score, p.renorm = int(bool(softmax)), int(bool(renorm))
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != E:
+            raise KernelError("moe_route: one bias per expert")
+        p.bias = bias.data_ptr()
     if w_gate is not None:
         _need(w_gate, "w_gate", torch.float32)
         if w_gate.numel() != x.shape[1] or dense.shape[1] < E + 1:

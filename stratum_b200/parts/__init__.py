@@ -1,5 +1,5 @@
-from . import (attention, block, delta_rule, differential_attention, embedding, latent_attention, mlp, moe, norm,  # noqa: F401
-               reentry, rope, sink_attention, state_space)  # noqa: F401  (registers the built-in parts)
+from . import (attention, block, delta_rule, differential_attention, embedding, latent_attention, linear_attention, mlp,  # noqa: F401
+               moe, norm, reentry, rope, sink_attention, state_space)  # noqa: F401  (registers the built-in parts)
 from .base import (Arrangement, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding,
                    RotaryTable, Runtime)
 from .registry import find_part, register_part, registered

@@ -179,6 +179,19 @@ class Embedding(Part):
         """int32 [T] -> float32 [T, hidden]."""
         raise NotImplementedError
 
+    def cache_spec(self) -> Optional[CacheSpec]:
+        """What the embedding keeps per sequence between steps (a StateSpec), or None: nothing."""
+        return None
+
+    def forward_step(self, step, cache: LayerCache, keep: bool = False) -> torch.Tensor:
+        """The embedded tokens of a step, float32 [T, hidden]; keep: the same rows are also left in step.embedded (a
+        tensor of their own: the stream is rewritten in place).  `cache` holds the embedding's state, if it keeps any.
+        The default gathers by token id alone."""
+        x = self.forward(step.token_ids)
+        if keep:       # a second gather, not a copy of the float32 rows
+            step.embedded = self.forward(step.token_ids)
+        return x
+
     def table(self) -> torch.Tensor:
         raise NotImplementedError
 

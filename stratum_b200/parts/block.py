@@ -46,6 +46,29 @@ class PreNormResidual(Arrangement):
         return None
 
 
+@register_part("arrangement", "parallel_residual")
+class ParallelResidual(Arrangement):
+    """x += mixer(norm_a(x)) + feed_forward(norm_b(x)): both sublayers read the same x, each through a norm of its own,
+    and both add into the stream.  Both norms run before either sublayer writes; where they are RMS norms of one size
+    and eps (which is what the library's models give) one kernel reads the row once, takes one sum of squares and
+    writes both outputs.  A layer may have no feed-forward."""
+    replays_prompts = True
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+    optional = ("feed_forward_norm", "feed_forward")
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
+        norm_a, mixer = layer.part("mixer_norm"), layer.part("mixer")
+        norm_b, ff = layer.part("feed_forward_norm"), layer.part("feed_forward")
+        if ff is None or norm_b is None:
+            mixer.forward(norm_a.forward(x), x, step, cache)
+            return
+        pair = getattr(norm_a, "forward_pair", None)
+        both = pair(x, norm_b) if pair is not None else None
+        xa, xb = both if both is not None else (norm_a.forward(x), norm_b.forward(x))
+        mixer.forward(xa, x, step, cache)
+        ff.forward(xb, x, step)
+
+
 class RoundedRows:
     """What an `output_norm_residual` layer asks of the layer in front of it: the rows of the residual stream
     rounded to the compute dtype, which its sublayers read.  (It stands where a layer's first norm stands in the

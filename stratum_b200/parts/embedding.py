@@ -1,6 +1,7 @@
 """Token embedding (a row gather, stratum/native/stratum_arch_llama.inc.c:564-593) and the output
 head (logits = W xn with W the head's own matrix if the file has one, else the embedding table,
-stratum/native/stratum_arch_llama.inc.c:722-723)."""
+stratum/native/stratum_arch_llama.inc.c:722-723); and an embedding that adds a row chosen by the token and the one in
+front of it."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -8,6 +9,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import kernels as K
+from ..cache.store import LayerCache, StateSpec
 from .base import Embedding, Head
 from .linear import STORE_F32, Linear
 from .registry import find_part, register_part
@@ -47,6 +49,52 @@ class TokenEmbedding(Embedding):
         K.embed_gather(self._table, token_ids, out)
         if self.norm is not None:
             self.norm.add_normed(out, out, accumulate=False)
+        return out
+
+
+@register_part("embedding", "pair_embedding")
+class PairEmbedding(Embedding):
+    """x = table[token] * scale + pairs[(previous * mul_prev + token * mul_cur) mod buckets]; a sequence's first token
+    reads the last row of `pairs` ([buckets + 1, hidden]).  The token in front of a step's first token is part of what
+    a sequence keeps between steps: one int per sequence in a state block of the cache, read and rewritten by the
+    kernel that gathers the rows, so that a decode step whose token ids are fed on the device needs nothing from the
+    host.  params: vocab, hidden, tensor (the table's name), pairs (the pair table's name), buckets, mul_prev,
+    mul_cur, scale."""
+    replays_prompts = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
+        self.name = spec.get("tensor") or self.prefix + "weight"
+        self.pairs_name = str(spec["pairs"])
+        self.buckets, self.mul_prev, self.mul_cur = int(spec["buckets"]), int(spec["mul_prev"]), int(spec["mul_cur"])
+        self.scale = float(spec.get("scale", 1.0))
+        self._table: Optional[torch.Tensor] = None
+        self._pairs: Optional[torch.Tensor] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.vocab, self.hidden)),
+                self.pairs_name: TensorSpec((self.buckets + 1, self.hidden))}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self._table, self._pairs = weights[self.name], weights[self.pairs_name]
+
+    def table(self) -> torch.Tensor:
+        return self._table
+
+    def cache_spec(self) -> StateSpec:
+        return StateSpec((1,), "int32")
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise ValueError("pair_embedding needs the step and its state: forward_step")
+
+    def forward_step(self, step, cache: LayerCache, keep: bool = False) -> torch.Tensor:
+        out = self.runtime.empty(step.n_tokens, self.hidden, dtype=torch.float32)
+        if keep:
+            step.embedded = self.runtime.empty(step.n_tokens, self.hidden, dtype=torch.float32)
+        K.embed_pairs(self._table, self._pairs, step.token_ids, step.token_pos, step.token_seq, step.seq_start,
+                      step.seq_slot, cache.state, out, step.embedded if keep else None, self.scale, self.mul_prev,
+                      self.mul_cur, cache.writes)
         return out
 
 

@@ -27,7 +27,9 @@ Variants, each a parameter: scores by softmax over all experts in sigmoid's plac
 they are, not divided by their sum (`renorm` false); no correction tensor (`correction` false); experts without a gate
 matrix, Wdown act(Wup h), with the activation named (`gated` false, `activation`); and a shared expert whose output is
 multiplied by sigmoid(w_sg . h), one number per token (`shared_gate`: the name of that row of weights): the router's
-kernel takes that dot product with the experts' and leaves the gate beside the experts' weights.
+kernel takes that dot product with the experts' and leaves the gate beside the experts' weights; and a bias on the
+router's logits (`router_bias`: tensor router.b).  Softmax scores over all experts, renormalised over the chosen ones,
+are the softmax over the chosen logits alone: a design that states its weights that way sets `score: softmax`.
 """
 from __future__ import annotations
 
@@ -55,8 +57,8 @@ GROUPED_MIN_ROWS = int(os.environ.get("STRATUM_MOE_GROUPED_MIN_ROWS", 96))
 class RoutedExperts(FeedForward):
     """params: hidden, n_experts, top, scale, n_groups, keep, intermediate (of an expert), shared_intermediate (of
     the shared expert; None: none), prefix; score ("sigmoid" or "softmax"), renorm, correction, gated, activation
-    ("silu", "gelu_tanh", "gelu_erf", "relu_sq"), shared_gate (tensor name under the prefix, or None).  Tensors:
-    router, correction, e<i>.gate / .up / .down, shared.gate / .up / .down (no .gate when not gated)."""
+    ("silu", "gelu_tanh", "gelu_erf", "relu_sq"), shared_gate (tensor name under the prefix, or None), router_bias.
+    Tensors: router, router.b, correction, e<i>.gate / .up / .down, shared.gate / .up / .down (no .gate when not gated)."""
     stores_output = True
 
     def __init__(self, spec, runtime):
@@ -83,7 +85,8 @@ class RoutedExperts(FeedForward):
                              + ("" if self.gated else " to experts without a gate"))
         self.act = GATE_ACTS[act]
         self.shared_gate = spec.get("shared_gate") if self.shared_ff else None
-        self.correction = self.w_gate = None
+        self.has_router_bias = bool(spec.get("router_bias", False))
+        self.correction = self.w_gate = self.router_bias = None
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -95,6 +98,8 @@ class RoutedExperts(FeedForward):
         t = {p + "router": TensorSpec((self.n_experts, H), role="vector")}
         if self.has_correction:
             t[p + "correction"] = TensorSpec((self.n_experts,), role="vector", init="zeros")
+        if self.has_router_bias:
+            t[p + "router.b"] = TensorSpec((self.n_experts,), role="vector", init="zeros")
         if self.shared_gate:
             t[p + self.shared_gate] = TensorSpec((1, H), role="vector")
         for e in self._experts():
@@ -111,6 +116,8 @@ class RoutedExperts(FeedForward):
             self.correction = weights[p + "correction"].contiguous()
         if self.shared_gate:
             self.w_gate = weights[p + self.shared_gate].reshape(-1).contiguous()
+        if self.has_router_bias:
+            self.router_bias = weights[p + "router.b"].contiguous()
         names = self._experts()
         ups = torch.cat([weights[p + e + "up"] for e in names], dim=0)
         # rows of an expert in the stacked first matrix: gate and up alternating, or the up matrix alone
@@ -133,7 +140,7 @@ class RoutedExperts(FeedForward):
         chosen = self.runtime.empty(T, self.top, dtype=torch.int32)
         weights = self.runtime.empty(T, self.top, dtype=torch.float32)
         K.moe_route(xin, self.router, self.correction, dense, chosen, weights, self.top, self.n_groups, self.keep,
-                    self.scale, softmax=self.softmax, renorm=self.renorm, w_gate=self.w_gate)
+                    self.scale, softmax=self.softmax, renorm=self.renorm, w_gate=self.w_gate, bias=self.router_bias)
         return dense, chosen, weights
 
     def _first(self, lin: Linear, x: torch.Tensor) -> torch.Tensor:

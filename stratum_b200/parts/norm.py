@@ -16,7 +16,8 @@ from .spec import TensorSpec
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps, prefix (e.g. "input_layernorm."; the gain is prefix + "weight") or tensor (the gain's whole
-    name), one_plus (the stored weight w is kept around zero and acts as 1 + w)."""
+    name), one_plus (the stored weight w is kept around zero and acts as 1 + w), scale (a constant factor on the
+    result, folded into the gain in float32 when it is bound: a factor on the logits rides on the last norm)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
@@ -25,6 +26,7 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.tensor = spec.get("tensor")
         self.one_plus = bool(spec.get("one_plus", False))
+        self.scale = float(spec.get("scale", 1.0))
         self.gain: Optional[torch.Tensor] = None
 
     @property
@@ -38,6 +40,8 @@ class RMSNorm(Norm):
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         w = weights[self.name]
         self.gain = (w + 1.0).contiguous() if self.one_plus else w
+        if self.scale != 1.0:
+            self.gain = (self.gain * self.scale).contiguous()
 
     def add_normed(self, y: torch.Tensor, residual: torch.Tensor, accumulate: bool = True,
                    copy: Optional[torch.Tensor] = None) -> None:

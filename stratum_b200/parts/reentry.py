@@ -1,4 +1,5 @@
-"""Re-entry of the embedded tokens into the residual stream at the head of a pass over looped layers.
+"""Re-entry of the embedded tokens into the residual stream at the head of a pass over looped layers: through a
+matrix (embedding_reentry), or by plain addition (embedding_readd, at the end of this file).
 
     x <- W [x ; x0] + b_t
 
@@ -49,3 +50,31 @@ class EmbeddingReentry(StreamOp):
         K.pack_columns(x, both, 0)
         K.pack_columns(step.embedded, both, H)
         self.lin(both, out=x, mode=STORE_F32)
+
+
+@register_part("stream_op", "embedding_readd")
+class EmbeddingReadd(StreamOp):
+    """x <- x + x0 + b_t at the head of a pass over looped layers, or x <- x + b_t where the embedded tokens are not
+    taken in again (`readd` false: the first pass).  b_t is row t of a table [passes, hidden].  params: hidden, rows
+    (of the table), row (this pass's), readd, prefix, table (the tensor's name, default "step")."""
+    replays_prompts = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden, self.rows, self.row = int(spec["hidden"]), int(spec["rows"]), int(spec["row"])
+        if not (0 <= self.row < self.rows):
+            raise ValueError(f"embedding_readd: row {self.row} outside a table of {self.rows}")
+        self.readd = bool(spec.get("readd", True))
+        self.t_name = self.prefix + str(spec.get("table", "step"))
+        self.vector: Optional[torch.Tensor] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.t_name: TensorSpec((self.rows, self.hidden), role="vector", init="zeros")}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.vector = weights[self.t_name][self.row].contiguous()
+
+    def forward(self, x: torch.Tensor, step) -> None:
+        if self.readd and step.embedded is None:
+            raise ValueError("embedding_readd needs the step's embedded tokens (ModelSpec.keep_embedded)")
+        K.add_rows(x, step.embedded if self.readd else None, self.vector)

@@ -25,6 +25,31 @@ from .base import PositionEncoding, RotaryTable
 from .registry import register_part
 
 
+def precise_frequencies(rope_dim: int, theta: float, scaling: Optional[dict]) -> (np.ndarray, float):
+    """The same table evaluated in float64 and rounded to float32 once, with the rescalings taken as written for any
+    positive factor (linear: inv_k / factor; yarn: the ramp and the magnitude 0.1 ln(factor) + 1)."""
+    n_pairs = rope_dim // 2
+    k = np.arange(n_pairs, dtype=np.float64)
+    base = float(theta) ** (-2.0 * k / float(rope_dim))
+    kind = (scaling or {}).get("kind", "none")
+    if kind in ("none", "default"):
+        return base.astype(np.float32), 1.0
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return (base / factor).astype(np.float32), 1.0
+    if kind == "yarn":
+        orig = float(scaling["original_max_position"])
+
+        def corr(turns: float) -> float:
+            return rope_dim * math.log(orig / (turns * 2.0 * math.pi)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(corr(float(scaling.get("beta_fast", 32.0)))), 0)
+        hi = min(math.ceil(corr(float(scaling.get("beta_slow", 1.0)))), rope_dim - 1)
+        ramp = np.clip((k - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return (base / factor * ramp + base * (1.0 - ramp)).astype(np.float32), 0.1 * math.log(factor) + 1.0
+    raise ValueError(f"rope scaling kind {kind!r} has no precise form")
+
+
 def inverse_frequencies(rope_dim: int, theta: float, scaling: Optional[dict]) -> (np.ndarray, float):
     """float32 inv_freq [rope_dim/2] and the magnitude factor for cos/sin."""
     n_pairs = rope_dim // 2
@@ -76,7 +101,8 @@ def inverse_frequencies(rope_dim: int, theta: float, scaling: Optional[dict]) ->
 
 @register_part("position", "rope")
 class RotaryEmbedding(PositionEncoding):
-    """params: rope_dim, theta, interleaved, scaling (dict with 'kind' and its numbers, or None)."""
+    """params: rope_dim, theta, interleaved, scaling (dict with 'kind' and its numbers, or None), precise (the table is
+    evaluated in float64 and rounded once, and a factor below one is taken as it stands)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
@@ -85,6 +111,7 @@ class RotaryEmbedding(PositionEncoding):
         self.theta = float(spec["theta"])
         self.interleaved = bool(spec.get("interleaved", False))
         self.scaling = spec.get("scaling")
+        self.precise = bool(spec.get("precise", False))
         self._table: Optional[RotaryTable] = None
 
     def pair_layout(self):
@@ -92,8 +119,9 @@ class RotaryEmbedding(PositionEncoding):
 
     def rotary(self) -> RotaryTable:
         if self._table is None:
-            inv, mag = inverse_frequencies(self.rope_dim, self.theta, self.scaling)
-            key = ("rope", self.rope_dim, self.theta, self.interleaved,
+            make = precise_frequencies if self.precise else inverse_frequencies
+            inv, mag = make(self.rope_dim, self.theta, self.scaling)
+            key = ("rope", self.rope_dim, self.theta, self.interleaved, self.precise,
                    tuple(sorted((self.scaling or {}).items())), str(self.runtime.device))
             self._table = RotaryTable(torch.from_numpy(inv).to(self.runtime.device), self.interleaved, mag, key)
         return self._table

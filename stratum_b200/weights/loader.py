@@ -79,6 +79,16 @@ def place(t: torch.Tensor, spec: TensorSpec, compute_dtype: torch.dtype, device)
     return t.to(device).to(dt).contiguous()
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor a model folder holds (headers only)."""
+    files = open_model_files(model_dir)
+    try:
+        return {n: tuple(e.shape) for f in files for n, e in f.entries.items()}
+    finally:
+        for f in files:
+            f.close()
+
+
 def load_weights(model_dir: str, expected: Mapping[str, TensorSpec], compute_dtype: torch.dtype,
                  device, ignored_suffixes: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """Read every expected tensor of a model folder onto the device."""
