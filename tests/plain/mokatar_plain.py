@@ -184,18 +184,22 @@ def gated_ff(W, pre, h):
     return linear(silu(linear(h, W[pre + "gate"])) * linear(h, W[pre + "up"]), W[pre + "down"])
 
 
-def route(f, W, pre, h):
-    """(chosen [T, top], weights [T, top]): the largest logits, and the softmax over those alone."""
+def route(f, W, pre, h, margins=None):
+    """(chosen [T, top], weights [T, top]): the largest logits, and the softmax over those alone.  margins (a list):
+    every token's gap between the last chosen logit and the best one left out is appended."""
     z = linear(h, W[pre + "router"], W[pre + "router.b"])
     top = f["router"]["top"]
     chosen = np.argsort(-z, axis=1, kind="stable")[:, :top]
+    if margins is not None and top < z.shape[1]:
+        ordered = -np.sort(-z, axis=1)
+        margins.extend((ordered[:, top - 1] - ordered[:, top]).tolist())
     zc = np.take_along_axis(z, chosen, axis=1)
     e = np.exp(zc - zc.max(axis=1, keepdims=True))
     return chosen, e / e.sum(axis=1, keepdims=True)
 
 
-def routed_ff(f, W, pre, h):
-    chosen, weights = route(f, W, pre, h)
+def routed_ff(f, W, pre, h, margins=None):
+    chosen, weights = route(f, W, pre, h, margins)
     out = np.zeros((h.shape[0], np.asarray(W[pre + "e0.down"]).shape[0]), F64)
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t], weights[t]):
@@ -203,21 +207,21 @@ def routed_ff(f, W, pre, h):
     return out
 
 
-def feed_forward(f, W, pre, h):
-    return gated_ff(W, pre, h) if f["kind"] == "dense" else routed_ff(f, W, pre, h)
+def feed_forward(f, W, pre, h, margins=None):
+    return gated_ff(W, pre, h) if f["kind"] == "dense" else routed_ff(f, W, pre, h, margins)
 
 
 # ---------------------------------------------------------------------------------------------- the model
 MIXERS = {"attention": attention, "attention_2": attention_2, "gla": gla}
 
 
-def layer(cfg, W, i, x):
+def layer(cfg, W, i, x, margins=None):
     entry = cfg["layers"][i]
     eps = cfg["norm"]["eps"]
     pre = f"l{i}."
     y = MIXERS[entry["type"]](entry["mixer"], W, pre + "mix.", rms_norm(x, W[pre + "norm1"], eps, True), eps)
     if entry.get("mlp") is not None:
-        y = y + feed_forward(entry["mlp"], W, pre + "mlp.", rms_norm(x, W[pre + "norm2"], eps, True))
+        y = y + feed_forward(entry["mlp"], W, pre + "mlp.", rms_norm(x, W[pre + "norm2"], eps, True), margins)
     return x + y
 
 
@@ -232,9 +236,9 @@ def runs(cfg):
     return out + [(i, None, False) for i in range(lp["stop"], n)]
 
 
-def forward(cfg, W, tokens, streams: Optional[List[np.ndarray]] = None):
+def forward(cfg, W, tokens, streams: Optional[List[np.ndarray]] = None, margins: Optional[list] = None):
     """Logits [T, vocab] of one sequence from its first token; streams (a list): the residual stream after every
-    layer run is appended."""
+    layer run is appended; margins (a list): every routing decision's gap between chosen and not chosen."""
     x0 = embed(cfg, W, tokens)
     x = x0.copy()
     for i, t, first in runs(cfg):
@@ -242,7 +246,7 @@ def forward(cfg, W, tokens, streams: Optional[List[np.ndarray]] = None):
             if t > 0:
                 x = x + x0
             x = x + np.asarray(W["loop.step"], F64)[t]
-        x = layer(cfg, W, i, x)
+        x = layer(cfg, W, i, x, margins)
         if streams is not None:
             streams.append(x.copy())
     xn = rms_norm(x, W["final.norm"], cfg["norm"]["eps"], True)
