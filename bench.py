@@ -6,6 +6,7 @@
     python bench.py --compare nibelorn      # the Nibelorn decoder beside a Llama decoder of equal size (one JSON line)
     python bench.py --compare dabodra       # the same for the Dabodra decoder
     python bench.py --compare vitinex       # the Vitinex decoder beside the Dabodra and the Llama decoder of equal size
+    python bench.py --compare mokatar       # the Mokatar decoder beside the same two
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
 sequence's cache filled to the given context at the end of the timed steps (so the timed steps
@@ -142,6 +143,42 @@ def vitinex_config(size, n_layers):
                                     "loop": {"start": 0, "stop": n_layers, "times": 1}})
 
 
+# --compare mokatar: the same widths, heads and vocabulary, beside the Dabodra decoder (the closest one here: attention
+# over a window with a sink, recurrent layers of fixed state, routed experts) and the Llama decoder.  Of every four
+# layers two are gated linear attention (a state of 128 x 128 per head, as the delta rule's), one is causal attention
+# with biases and a zero sink, one is attention over a window of 1,024 that keeps the first four tokens; the
+# feed-forwards alternate between eight routed experts of which a token uses two and a dense one, sized so that a
+# token's active feed-forward weights equal the Llama decoder's SwiGLU (2 x ff = llama_inner).  The whole stack is one
+# loop that runs once: the pass's vector is added in every step.
+MOKATAR_SIZES = {
+    "1b": {"dim": 128, "vdim": 128, "window": 1024, "keep": 4, "gla_dim": 128, "gla_vdim": 128, "rank": 64,
+           "experts": 8, "top": 2, "ff": 2752},
+    "8b": {"dim": 128, "vdim": 128, "window": 1024, "keep": 4, "gla_dim": 128, "gla_vdim": 128, "rank": 64,
+           "experts": 8, "top": 2, "ff": 5440},
+}
+
+
+def mokatar_config(size, n_layers):
+    from stratum_b200.config import MokatarConfig
+    z, m = COMPARE_SIZES[size], MOKATAR_SIZES[size]
+    win = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["dim"] ** -0.5,
+           "mask": {"size": m["window"], "keep_first": m["keep"]},
+           "rot": {"base": 10000.0, "dims": m["dim"] // 2,
+                   "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    full = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["dim"] ** -0.5,
+            "rot": {"base": 10000.0, "dims": m["dim"], "scaling": {"factor": 2.0}}}
+    rec = {"heads": z["heads"], "dim": m["gla_dim"], "vdim": m["gla_vdim"], "tau": 16.0, "rank": m["rank"]}
+    moe = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"]}}
+    dense = {"kind": "dense", "ff": z["llama_inner"]}
+    kinds = [("gla", rec), ("attention_2", full), ("gla", rec), ("attention", win)]
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": dense if i % 2 else moe}
+              for i in range(n_layers)]
+    return MokatarConfig.from_dict({
+        "architecture": "Mokatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+        "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+        "layers": layers, "loop": {"start": 0, "stop": n_layers, "times": 1}})
+
+
 def llama_like(size, n_layers):
     from stratum_b200.config import LlamaConfig
     z = COMPARE_SIZES[size]
@@ -181,8 +218,8 @@ def kernel_times(llm, batch, context, prefill_tokens, vocab, rng):
 
 
 def compare_models(args, rng):
-    """Prefill and decode throughput of the Nibelorn, the Dabodra or the Vitinex decoder beside a Llama decoder of equal
-    size (the Vitinex decoder also beside the Dabodra decoder): one
+    """Prefill and decode throughput of the Nibelorn, the Dabodra, the Vitinex or the Mokatar decoder beside a Llama
+    decoder of equal size (the Vitinex and the Mokatar decoder also beside the Dabodra decoder): one
     prompt of --prefill-tokens, and decode steps of --batch sequences at --context tokens (random bf16 weights,
     device-timed as the main workload is); with --kernels also the device time of every kernel of one prompt and one
     decode step.  One JSON line."""
@@ -190,8 +227,9 @@ def compare_models(args, rng):
     from stratum_b200 import Stratum
     n_layers = args.layers or 8
     which = args.compare
-    make = {"nibelorn": nibelorn_config, "dabodra": dabodra_config, "vitinex": vitinex_config}[which]
-    others = [("llama", llama_like)] + ([("dabodra", dabodra_config)] if which == "vitinex" else [])
+    make = {"nibelorn": nibelorn_config, "dabodra": dabodra_config, "vitinex": vitinex_config,
+            "mokatar": mokatar_config}[which]
+    others = [("llama", llama_like)] + ([("dabodra", dabodra_config)] if which in ("vitinex", "mokatar") else [])
     out = {"compare": which, "layers": n_layers, "batch": args.batch, "context": args.context,
            "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic: random-init weights",
            "sizes": {}}
@@ -449,9 +487,9 @@ def main() -> int:
                     help="prompt length of --prefill-only (the default JSON line always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
-    ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra", "vitinex"],
-                    help="instead of the main workload: prefill and decode throughput of the Nibelorn, the Dabodra or "
-                         "the Vitinex decoder beside a Llama decoder of equal size (Vitinex also beside Dabodra), at 1B-like and 8B-like layer sizes (--layers of "
+    ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra", "vitinex", "mokatar"],
+                    help="instead of the main workload: prefill and decode throughput of the Nibelorn, the Dabodra, "
+                         "the Vitinex or the Mokatar decoder beside a Llama decoder of equal size (Vitinex and Mokatar also beside Dabodra), at 1B-like and 8B-like layer sizes (--layers of "
                          "them, default 8)")
     ap.add_argument("--kernels", action="store_true",
                     help="with --compare: also the device time of every kernel of one prompt and one decode step")

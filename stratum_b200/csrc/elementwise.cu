@@ -114,10 +114,31 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
   }
 }
 
+// the same on four neighbouring values a thread (hidden % 4 == 0, 16-byte aligned rows); n4 counts float4s
+__global__ void add_rows_vec_kernel(float4* __restrict__ x, const float4* __restrict__ a,
+                                    const float4* __restrict__ row, size_t n4, int hidden4) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    float4 v = ld_fresh(x + i);
+    if (a) {
+      const float4 w = ld_fresh(a + i);
+      v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    const float4 r = row[i % hidden4];
+    x[i] = make_float4(v.x + r.x, v.y + r.y, v.z + r.z, v.w + r.w);
+  }
+}
+
 STRATUM_EXPORT int stratum_add_rows(float* x, const float* a, const float* row, int n_tokens, int hidden,
                                     cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t n = (size_t)n_tokens * hidden;
+  if (hidden % 4 == 0 && ((((uintptr_t)x | (uintptr_t)a | (uintptr_t)row) & 15) == 0)) {
+    const size_t blocks = (n / 4 + 255) / 256;
+    return launch_pdl(add_rows_vec_kernel, (unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, stream,
+                      (float4*)x, (const float4*)a, (const float4*)row, n / 4, hidden / 4);
+  }
   const size_t blocks = (n + 255) / 256;
   return launch_pdl(add_rows_kernel, (unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, stream, x, a, row, n,
                     hidden);
@@ -229,6 +250,113 @@ STRATUM_EXPORT int stratum_rmsnorm(const float* x, const float* gain, const int*
   if (n_rows <= 0) return 0;
   if (out_dtype == STRATUM_DT_F32) return launch_rmsnorm<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, stream);
   if (out_dtype == STRATUM_DT_BF16) return launch_rmsnorm<bf16>(x, gain, rows, (bf16*)out, n_rows, hidden, eps, stream);
+  return STRATUM_ERR_DTYPE;
+}
+
+// Two norms of the same rows with a gain each (the two sublayers of a layer that both read the stream): the row is
+// read once and its sum of squares taken once.  The sum's order is that of the one-output kernels of the same shape.
+template <typename T>
+__global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ gain_a,
+                                    const float* __restrict__ gain_b, T* __restrict__ out_a, T* __restrict__ out_b,
+                                    int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const float* xr = x + (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = ld_fresh(xr + i);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* oa = out_a + (size_t)blockIdx.x * hidden;
+  T* ob = out_b + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = ld_fresh(xr + i) * scale;
+    oa[i] = from_float<T>(v * gain_a[i]);
+    ob[i] = from_float<T>(v * gain_b[i]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_four(T* o, int i, float a, float b, float c, float d) {
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(o)[i] = make_float4(a, b, c, d);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(o)[i] = pk;
+  }
+}
+
+template <typename T, int VPT>
+__global__ void rmsnorm_pair_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain_a,
+                                        const float* __restrict__ gain_b, T* __restrict__ out_a,
+                                        T* __restrict__ out_b, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  const int n4 = hidden >> 2;
+  pdl_wait();
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * hidden);
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int i = threadIdx.x + j * blockDim.x;
+    v[j] = i < n4 ? ld_fresh(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+    ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* oa = out_a + (size_t)blockIdx.x * hidden;
+  T* ob = out_b + (size_t)blockIdx.x * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i >= n4) continue;
+    const float4 ga = reinterpret_cast<const float4*>(gain_a)[i], gb = reinterpret_cast<const float4*>(gain_b)[i];
+    const float a = v[j].x * scale, b = v[j].y * scale, c = v[j].z * scale, d = v[j].w * scale;
+    store_four<T>(oa, i, a * ga.x, b * ga.y, c * ga.z, d * ga.w);
+    store_four<T>(ob, i, a * gb.x, b * gb.y, c * gb.z, d * gb.w);
+  }
+}
+
+template <typename T>
+static int launch_rmsnorm_pair(const float* x, const float* ga, const float* gb, T* oa, T* ob, int n_rows, int hidden,
+                               float eps, cudaStream_t stream) {
+  const bool vec = hidden % 4 == 0 &&
+                   ((((uintptr_t)x | (uintptr_t)ga | (uintptr_t)gb | (uintptr_t)oa | (uintptr_t)ob) & 15) == 0);
+  if (vec && hidden <= 4 * 4 * 1024) {
+    // block shapes as launch_rmsnorm picks them: by the row's length alone on the float32 path
+    const int n4 = hidden / 4;
+    const bool few = n_rows < 256 || sizeof(T) == 4;
+#define PAIR_VEC(V)                                                                                          \
+  launch_pdl(rmsnorm_pair_vec_kernel<T, V>, n_rows, (((n4 + V - 1) / V + 31) / 32) * 32, 0, stream, x, ga, gb, oa, ob, \
+             hidden, eps)
+    if (few && n4 <= 1024) return PAIR_VEC(1);
+    if (few) return PAIR_VEC(4);
+    if (n4 <= 256) return PAIR_VEC(1);
+    if (n4 <= 512) return PAIR_VEC(2);
+    if (n4 <= 1024) return PAIR_VEC(8);
+    return PAIR_VEC(4);
+#undef PAIR_VEC
+  }
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  return launch_pdl(rmsnorm_pair_kernel<T>, n_rows, threads, 0, stream, x, ga, gb, oa, ob, hidden, eps);
+}
+
+STRATUM_EXPORT int stratum_rmsnorm_pair(const float* x, const float* gain_a, const float* gain_b, void* out_a,
+                                        void* out_b, int out_dtype, int n_rows, int hidden, float eps,
+                                        cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (out_dtype == STRATUM_DT_F32)
+    return launch_rmsnorm_pair<float>(x, gain_a, gain_b, (float*)out_a, (float*)out_b, n_rows, hidden, eps, stream);
+  if (out_dtype == STRATUM_DT_BF16)
+    return launch_rmsnorm_pair<bf16>(x, gain_a, gain_b, (bf16*)out_a, (bf16*)out_b, n_rows, hidden, eps, stream);
   return STRATUM_ERR_DTYPE;
 }
 

@@ -3,8 +3,10 @@
 //
 // Per token, from the float32 sums of the fused input projection (row = [q | k | v | g | a]: n_heads * dim twice,
 // n_heads * vdim twice, then `rank` values of the decay's inner projection):
-//   prep      z = W_a2 a + b  (n_heads * dim channels, float32 sums in the order of `rank`);
-//             alpha = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau), the logarithm taken without forming sigmoid(z).
+//   cast      the `rank` values a go, rounded to the compute dtype, to a matrix of their own: the operand of the decay's
+//             second projection z = W_a2 a + b, which is a matrix product like any other (float32 sums);
+//   decay     alpha = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau), in place, the logarithm taken without forming
+//             sigmoid(z);
 //   recur     per head, token after token:  S <- diag(alpha) S + k v^T;  o = S^T q * dim^(-1/2)
 //             (the decay acts on the rows of S, which belong to key channels; o sees the token's own write).
 //   finish    o / sqrt(mean_vdim(o^2) + eps) * gain * silu(g), rounded to the compute dtype for the output product.
@@ -21,10 +23,10 @@
 
 struct Gla {
   const float* proj;        // [tokens][ld]
-  const void* w_a2;         // [n_heads * dim][rank], the compute dtype
-  const float* b_a2;        // [n_heads * dim]
+  void* inner;              // [tokens][ld_inner], the compute dtype: the decay's inner projection (cast)
+  const float* reserved_p;
   const float* gain;        // [vdim]
-  float* alpha;             // [tokens][n_heads * dim]
+  float* alpha;             // [tokens][n_heads * dim]: z when `decay` begins, alpha when it ends
   float* o_raw;             // [tokens][n_heads * vdim]
   void* out;                // [tokens][ldo] compute dtype
   float* state;             // [slots][state_stride]: S^T [n_heads][vdim][dim]
@@ -33,32 +35,33 @@ struct Gla {
   const int* seq_slot;      // [seqs]
   int ld, ldo, n_tokens, n_seqs;
   int n_heads, dim, vdim, rank;
-  int state_stride, write_state;
+  int state_stride, write_state, ld_inner, reserved_i;
   float eps, inv_tau, q_scale, reserved;
 };
 
 __device__ __forceinline__ float gla_silu(float z) { return z / (1.0f + expf(-z)); }
 
-// ---------------------------------------------------------------- prep: one block per token
-#define GLA_PREP_THREADS 256
+// ---------------------------------------------------------------- cast and decay: elementwise
 template <typename T>
-__global__ void __launch_bounds__(GLA_PREP_THREADS) gla_prep_kernel(const Gla P) {
-  extern __shared__ float gla_a[];                   // [rank]
+__global__ void __launch_bounds__(256) gla_cast_kernel(const Gla P) {
   pdl_trigger();
   pdl_wait();                                        // the projection is the work of the kernel before: ld_fresh
-  const int t = blockIdx.x;
-  const int HD = P.n_heads * P.dim, R = P.rank;
-  const float* a = P.proj + (size_t)t * P.ld + 2 * (size_t)HD + 2 * (size_t)P.n_heads * P.vdim;
-  for (int r = threadIdx.x; r < R; r += GLA_PREP_THREADS) gla_a[r] = ld_fresh(a + r);
-  __syncthreads();
-  float* out = P.alpha + (size_t)t * HD;
-  for (int c = threadIdx.x; c < HD; c += GLA_PREP_THREADS) {
-    const T* w = (const T*)P.w_a2 + (size_t)c * R;
-    float z = 0.f;
-    for (int r = 0; r < R; r++) z = fmaf(to_float(w[r]), gla_a[r], z);
-    z += P.b_a2[c];
+  const size_t n = (size_t)P.n_tokens * P.rank;
+  const size_t first = 2 * (size_t)P.n_heads * P.dim + 2 * (size_t)P.n_heads * P.vdim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / P.rank, r = i - t * P.rank;
+    ((T*)P.inner)[t * P.ld_inner + r] = from_float<T>(ld_fresh(P.proj + t * P.ld + first + r));
+  }
+}
+
+__global__ void __launch_bounds__(256) gla_decay_kernel(const Gla P) {
+  pdl_trigger();
+  pdl_wait();                                        // z is the work of the kernel before: ld_fresh
+  const size_t n = (size_t)P.n_tokens * P.n_heads * P.dim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float z = ld_fresh(P.alpha + i);
     const float ls = z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z));      // log sigmoid(z)
-    out[c] = expf(ls * P.inv_tau);
+    P.alpha[i] = expf(ls * P.inv_tau);
   }
 }
 
@@ -226,9 +229,28 @@ static int gla_check(const Gla& P) {
   if (P.ld < 2 * P.n_heads * P.dim + 2 * P.n_heads * P.vdim + P.rank || P.ldo < P.n_heads * P.vdim)
     return STRATUM_ERR_SHAPE;
   if (P.state_stride < P.n_heads * P.dim * P.vdim) return STRATUM_ERR_SHAPE;
-  if (P.dim > 32 * GLA_ROWS || P.rank > 8192) return STRATUM_ERR_LIMIT;
+  if (P.dim > 32 * GLA_ROWS) return STRATUM_ERR_LIMIT;
   if (P.n_heads > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
   return 0;
+}
+
+static unsigned gla_blocks(size_t n) {
+  const size_t blocks = (n + 255) / 256;
+  return (unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks);
+}
+
+// The decay's inner projection as a matrix of the compute dtype (one launch).
+STRATUM_EXPORT int stratum_gla_cast(const Gla* params, int dtype, cudaStream_t stream) {
+  const Gla& P = *params;
+  if (P.n_tokens <= 0) return 0;
+  const int bad = gla_check(P);
+  if (bad) return bad;
+  if (!P.inner || P.ld_inner < P.rank) return STRATUM_ERR_SHAPE;
+  const unsigned blocks = gla_blocks((size_t)P.n_tokens * P.rank);
+  if (dtype == STRATUM_DT_F32) launch_pdl(gla_cast_kernel<float>, blocks, 256, 0, stream, P);
+  else if (dtype == STRATUM_DT_BF16) launch_pdl(gla_cast_kernel<bf16>, blocks, 256, 0, stream, P);
+  else return STRATUM_ERR_DTYPE;
+  return launch_status();
 }
 
 template <int L>
@@ -238,30 +260,32 @@ static void gla_recur_launch(const Gla& P, cudaStream_t stream) {
   gla_recur_kernel<L><<<grid, GLA_THREADS, 0, stream>>>(P);
 }
 
-// Everything of a step: prep, recurrence, finish (three launches).  dtype: the compute dtype (of w_a2 and `out`).
-STRATUM_EXPORT int stratum_gla(const Gla* params, int dtype, cudaStream_t stream) {
+// The rest of a step, one launch each: which = 0 the decays from z (in place), 1 the recurrence, 2 finish.  dtype:
+// the compute dtype of `out`.
+STRATUM_EXPORT int stratum_gla(const Gla* params, int which, int dtype, cudaStream_t stream) {
   const Gla& P = *params;
   if (P.n_tokens <= 0 || P.n_seqs <= 0) return 0;
   const int bad = gla_check(P);
   if (bad) return bad;
   if (dtype != STRATUM_DT_F32 && dtype != STRATUM_DT_BF16) return STRATUM_ERR_DTYPE;
-  const size_t smem = (size_t)P.rank * sizeof(float);
-  if (dtype == STRATUM_DT_F32) launch_pdl(gla_prep_kernel<float>, P.n_tokens, GLA_PREP_THREADS, smem, stream, P);
-  else launch_pdl(gla_prep_kernel<bf16>, P.n_tokens, GLA_PREP_THREADS, smem, stream, P);
-  int st = launch_status();
-  if (st) return st;
-  int L = 1;
-  while (GLA_ROWS * L < P.dim) L <<= 1;
-  switch (L) {
-    case 1: gla_recur_launch<1>(P, stream); break;
-    case 2: gla_recur_launch<2>(P, stream); break;
-    case 4: gla_recur_launch<4>(P, stream); break;
-    case 8: gla_recur_launch<8>(P, stream); break;
-    case 16: gla_recur_launch<16>(P, stream); break;
-    default: gla_recur_launch<32>(P, stream); break;
+  if (which == 0) {
+    launch_pdl(gla_decay_kernel, gla_blocks((size_t)P.n_tokens * P.n_heads * P.dim), 256, 0, stream, P);
+    return launch_status();
   }
-  st = launch_status();
-  if (st) return st;
+  if (which == 1) {
+    int L = 1;
+    while (GLA_ROWS * L < P.dim) L <<= 1;
+    switch (L) {
+      case 1: gla_recur_launch<1>(P, stream); break;
+      case 2: gla_recur_launch<2>(P, stream); break;
+      case 4: gla_recur_launch<4>(P, stream); break;
+      case 8: gla_recur_launch<8>(P, stream); break;
+      case 16: gla_recur_launch<16>(P, stream); break;
+      default: gla_recur_launch<32>(P, stream); break;
+    }
+    return launch_status();
+  }
+  if (which != 2) return STRATUM_ERR_SHAPE;
   const long long items = (long long)P.n_tokens * P.n_heads;
   const long long blocks = (items + 3) / 4;
   if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;

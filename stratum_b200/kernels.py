@@ -220,6 +220,20 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
              c_float(eps), _stream()), "rmsnorm")
 
 
+def rmsnorm_pair(x: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, eps: float, out_a: torch.Tensor,
+                 out_b: torch.Tensor) -> None:
+    """out_a[r] = rmsnorm(x[r]) * gain_a and out_b[r] = rmsnorm(x[r]) * gain_b from one pass over x (float32 [rows, H];
+    the outputs of one dtype)."""
+    _need(x, "x", torch.float32); _need(gain_a, "gain_a", torch.float32); _need(gain_b, "gain_b", torch.float32)
+    _need(out_a, "out_a"); _need(out_b, "out_b", out_a.dtype)
+    if out_a.shape != x.shape or out_b.shape != x.shape or gain_a.numel() != x.shape[1] or gain_b.numel() != x.shape[1]:
+        raise KernelError("rmsnorm_pair: shapes disagree")
+    f = _fn("elementwise", "stratum_rmsnorm_pair",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(x), _ptr(gain_a), _ptr(gain_b), _ptr(out_a), _ptr(out_b), dtype_code(out_a.dtype), x.shape[0],
+             x.shape[1], c_float(eps), _stream()), "rmsnorm_pair")
+
+
 def rmsnorm_heads(x: torch.Tensor, first_col: int, n_heads: int, head_dim: int, gain: torch.Tensor,
                   eps: float) -> None:
     """In place, in every row of x [T, width]: each of the n_heads stretches of head_dim values from column
@@ -1026,45 +1040,75 @@ def ssm_scan(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, a_l
 # ------------------------------------------------------------------ gated linear attention
 class _Gla(ctypes.Structure):
     """Mirror of struct Gla in csrc/gla.cu."""
-    _fields_ = [("proj", c_void_p), ("w_a2", c_void_p), ("b_a2", c_void_p), ("gain", c_void_p), ("alpha", c_void_p),
-                ("o_raw", c_void_p), ("out", c_void_p), ("state", c_void_p), ("token_seq", c_void_p),
-                ("seq_start", c_void_p), ("seq_slot", c_void_p),
+    _fields_ = [("proj", c_void_p), ("inner", c_void_p), ("reserved_p", c_void_p), ("gain", c_void_p),
+                ("alpha", c_void_p), ("o_raw", c_void_p), ("out", c_void_p), ("state", c_void_p),
+                ("token_seq", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p),
                 ("ld", c_int), ("ldo", c_int), ("n_tokens", c_int), ("n_seqs", c_int),
                 ("n_heads", c_int), ("dim", c_int), ("vdim", c_int), ("rank", c_int),
-                ("state_stride", c_int), ("write_state", c_int),
+                ("state_stride", c_int), ("write_state", c_int), ("ld_inner", c_int), ("reserved_i", c_int),
                 ("eps", c_float), ("inv_tau", c_float), ("q_scale", c_float), ("reserved", c_float)]
 
 
-def gla(proj: torch.Tensor, w_a2: torch.Tensor, b_a2: torch.Tensor, gain: torch.Tensor, alpha: torch.Tensor,
-        o_raw: torch.Tensor, out: torch.Tensor, state: torch.Tensor, token_seq: torch.Tensor, seq_start: torch.Tensor,
-        seq_slot: torch.Tensor, n_heads: int, dim: int, vdim: int, tau: float, q_scale: float, eps: float,
-        write_state: bool = True) -> None:
-    """Gated linear attention over a step (see csrc/gla.cu): proj float32 [tokens, >= 2 heads dim + 2 heads vdim +
-    rank] holds q | k | v | g | the decay's inner projection; w_a2 [heads * dim, rank] in out's dtype, b_a2 float32;
-    alpha float32 [tokens, heads * dim] and o_raw float32 [tokens, heads * vdim] are scratch; state float32 [slots,
-    >= heads * vdim * dim] holds every sequence's S^T; out [tokens, >= heads * vdim] receives the normed, gated
-    read-out in the compute dtype."""
-    _need(proj, "proj", torch.float32, contiguous=False); _need(w_a2, "w_a2", out.dtype)
-    _need(b_a2, "b_a2", torch.float32); _need(gain, "gain", torch.float32); _need(alpha, "alpha", torch.float32)
-    _need(o_raw, "o_raw", torch.float32); _need(out, "out", contiguous=False); _need(state, "state", torch.float32)
-    _need(token_seq, "token_seq", torch.int32); _need(seq_start, "seq_start", torch.int32)
-    _need(seq_slot, "seq_slot", torch.int32)
-    T = proj.shape[0]
-    if (w_a2.shape[0] != n_heads * dim or b_a2.numel() != n_heads * dim or gain.numel() != vdim
-            or alpha.shape != (T, n_heads * dim) or o_raw.shape != (T, n_heads * vdim) or out.shape[0] != T
-            or state.dim() != 2):
-        raise KernelError("gla: shapes disagree")
-    p = _Gla()
-    p.proj, p.w_a2, p.b_a2, p.gain = proj.data_ptr(), w_a2.data_ptr(), b_a2.data_ptr(), gain.data_ptr()
-    p.alpha, p.o_raw, p.out, p.state = alpha.data_ptr(), o_raw.data_ptr(), out.data_ptr(), state.data_ptr()
-    p.token_seq, p.seq_start, p.seq_slot = token_seq.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr()
-    p.ld, p.ldo, p.n_tokens, p.n_seqs = proj.stride(0), out.stride(0), T, seq_slot.numel()
-    p.n_heads, p.dim, p.vdim, p.rank = n_heads, dim, vdim, w_a2.shape[1]
-    p.state_stride, p.write_state = state.stride(0), int(bool(write_state))
-    p.eps, p.inv_tau, p.q_scale = float(eps), 1.0 / float(tau), float(q_scale)
-    f = _fn("gla", "stratum_gla", [c_void_p, c_int, c_void_p])
-    _check(f(ctypes.addressof(p), dtype_code(out.dtype), _stream()), "gla")
-    count_launches(2)          # prep, recurrence and finish are three launches
+class GlaStep:
+    """One step of gated linear attention over a fused projection (see csrc/gla.cu): proj float32 [tokens, >= 2 heads
+    dim + 2 heads vdim + rank] holds q | k | v | g | the decay's inner projection.  In order: `cast(inner)` leaves the
+    inner projection in a matrix of the compute dtype [tokens, >= rank]; the caller's matrix product turns it into z
+    float32 [tokens, heads * dim]; `decay(z)` makes the decays of z in place; `recur(...)` runs the recurrence over
+    every sequence's state (float32 [slots, >= heads * vdim * dim], S^T) and leaves the read-outs in o_raw float32
+    [tokens, heads * vdim]; `finish(...)` norms and gates them into out (compute dtype [tokens, >= heads * vdim])."""
+
+    def __init__(self, proj: torch.Tensor, n_heads: int, dim: int, vdim: int, rank: int, tau: float, q_scale: float,
+                 eps: float):
+        _need(proj, "proj", torch.float32, contiguous=False)
+        p = self.p = _Gla()
+        p.proj, p.ld, p.n_tokens = proj.data_ptr(), proj.stride(0), proj.shape[0]
+        p.n_heads, p.dim, p.vdim, p.rank = n_heads, dim, vdim, rank
+        p.state_stride = n_heads * dim * vdim           # until recur() is told the real one
+        p.ldo = n_heads * vdim
+        p.eps, p.inv_tau, p.q_scale = float(eps), 1.0 / float(tau), float(q_scale)
+        p.n_seqs = 1
+        self.T, self.keep = proj.shape[0], [proj]
+
+    def cast(self, inner: torch.Tensor) -> None:
+        _need(inner, "inner", contiguous=False)
+        if inner.shape[0] != self.T or inner.shape[1] < self.p.rank or inner.stride(1) != 1:
+            raise KernelError("gla: the inner projection's matrix and the step disagree")
+        self.p.inner, self.p.ld_inner = inner.data_ptr(), inner.stride(0)
+        f = _fn("gla", "stratum_gla_cast", [c_void_p, c_int, c_void_p])
+        _check(f(ctypes.addressof(self.p), dtype_code(inner.dtype), _stream()), "gla_cast")
+
+    def _run(self, which: int, dtype: torch.dtype, what: str) -> None:
+        f = _fn("gla", "stratum_gla", [c_void_p, c_int, c_int, c_void_p])
+        _check(f(ctypes.addressof(self.p), which, dtype_code(dtype), _stream()), what)
+
+    def decay(self, z: torch.Tensor) -> None:
+        _need(z, "z", torch.float32)
+        if z.shape != (self.T, self.p.n_heads * self.p.dim):
+            raise KernelError("gla: z and the step disagree")
+        self.p.alpha = z.data_ptr()
+        self.keep.append(z)
+        self._run(0, torch.float32, "gla_decay")
+
+    def recur(self, o_raw: torch.Tensor, state: torch.Tensor, token_seq: torch.Tensor, seq_start: torch.Tensor,
+              seq_slot: torch.Tensor, write_state: bool = True) -> None:
+        _need(o_raw, "o_raw", torch.float32); _need(state, "state", torch.float32)
+        _need(token_seq, "token_seq", torch.int32); _need(seq_start, "seq_start", torch.int32)
+        _need(seq_slot, "seq_slot", torch.int32)
+        p = self.p
+        if o_raw.shape != (self.T, p.n_heads * p.vdim) or state.dim() != 2 or not p.alpha:
+            raise KernelError("gla: shapes disagree, or the decays were not made")
+        p.o_raw, p.state, p.state_stride = o_raw.data_ptr(), state.data_ptr(), state.stride(0)
+        p.token_seq, p.seq_start, p.seq_slot = token_seq.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr()
+        p.n_seqs, p.write_state = seq_slot.numel(), int(bool(write_state))
+        self._run(1, torch.float32, "gla_recur")
+
+    def finish(self, gain: torch.Tensor, out: torch.Tensor) -> None:
+        _need(gain, "gain", torch.float32); _need(out, "out", contiguous=False)
+        p = self.p
+        if gain.numel() != p.vdim or out.shape[0] != self.T or out.shape[1] < p.n_heads * p.vdim or not p.o_raw:
+            raise KernelError("gla: shapes disagree, or the recurrence has not run")
+        p.gain, p.out, p.ldo = gain.data_ptr(), out.data_ptr(), out.stride(0)
+        self._run(2, out.dtype, "gla_finish")
 
 
 # ------------------------------------------------------------------ routed experts

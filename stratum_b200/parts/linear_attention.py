@@ -8,8 +8,9 @@ per key channel, alpha = sigmoid(Wa2 (Wa1 h) + b)^(1/tau) ([heads][d]; Wa1 maps 
     o <- o / sqrt(mean(o^2) + eps) * gain * silu(Wg h)_j;      result = Wo concat_j(o)
 
 What a sequence keeps between steps is S: a block of fixed size per sequence (cache.StateSpec), whatever its length.
-The five projections that read h run as one product with float32 sums; everything between them and the output
-product is float32, the decay's second projection included (csrc/gla.cu).
+The five projections that read h run as one product with float32 sums; the decay's inner values go, rounded to the
+compute dtype, through its second projection (a matrix product with float32 sums); everything from there to the
+output product is float32 (csrc/gla.cu).
 """
 from __future__ import annotations
 
@@ -62,7 +63,7 @@ class GatedLinearAttention(Mixer):
         stack = [weights[n[k]] for k in ("q", "k", "v", "g", "a1")]
         self.w_in = Linear(self.runtime, torch.cat(stack, dim=0).contiguous())
         self.w_o = Linear(self.runtime, weights[n["o"]])
-        self.w_a2, self.b_a2 = weights[n["a2"]].contiguous(), weights[n["a2"] + ".b"].contiguous()
+        self.w_a2 = Linear(self.runtime, weights[n["a2"]].contiguous(), weights[n["a2"] + ".b"].contiguous())
         self.gain = weights[n["norm"]].contiguous()
 
     def cache_spec(self) -> StateSpec:
@@ -73,9 +74,14 @@ class GatedLinearAttention(Mixer):
         f32 = torch.float32
         proj = self.runtime.empty(T, padded(self.width), dtype=f32)
         self.w_in(xin, out=proj[:, :self.width], mode=STORE_F32)
+        step_ = K.GlaStep(proj, self.n_heads, self.d, self.dv, self.rank, self.tau, self.q_scale, self.eps)
+        inner = self.runtime.empty(T, padded(self.rank))
+        step_.cast(inner)
         alpha = self.runtime.empty(T, self.qk_cols, dtype=f32)
+        self.w_a2(inner[:, :self.rank], out=alpha, mode=STORE_F32)
+        step_.decay(alpha)
         o_raw = self.runtime.empty(T, self.v_cols, dtype=f32)
+        step_.recur(o_raw, cache.state, step.token_seq, step.seq_start, step.seq_slot, cache.writes)
         out = self.runtime.empty(T, padded(self.v_cols))
-        K.gla(proj, self.w_a2, self.b_a2, self.gain, alpha, o_raw, out, cache.state, step.token_seq, step.seq_start,
-              step.seq_slot, self.n_heads, self.d, self.dv, self.tau, self.q_scale, self.eps, cache.writes)
+        step_.finish(self.gain, out)
         self.w_o(out[:, :self.v_cols], out=residual, mode=STORE_F32 if store else ADD_TO_F32)

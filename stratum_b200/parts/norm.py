@@ -53,6 +53,15 @@ class RMSNorm(Norm):
         K.rmsnorm(x, self.gain, self.eps, out, rows)
         return out
 
+    def forward_pair(self, x: torch.Tensor, other: Norm):
+        """This norm's and `other`'s output on the same rows from one pass over them, or None where the two are not
+        RMS norms of one size and eps (the caller then runs each by itself)."""
+        if not isinstance(other, RMSNorm) or other.size != self.size or other.eps != self.eps:
+            return None
+        out_a, out_b = self.runtime.empty(x.shape[0], self.size), self.runtime.empty(x.shape[0], self.size)
+        K.rmsnorm_pair(x, self.gain, other.gain, self.eps, out_a, out_b)
+        return out_a, out_b
+
     def handover(self) -> Optional[Handover]:
         # the matrix products that can honour it are the bfloat16 ones; sums of squares are kept per 128 columns
         if self.runtime is None or self.runtime.dtype != torch.bfloat16 or self.size % 128 != 0:

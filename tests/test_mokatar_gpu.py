@@ -72,11 +72,16 @@ def test_gla_kernels(heads, dim, vdim, rank, long):
         rows_ = np.concatenate([proj[i][done[i]:done[i] + cut[i]] for i in range(2)])
         T = rows_.shape[0]
         seq = np.concatenate([np.full(cut[i], i) for i in range(2)])
-        alpha = torch.empty(T, HD, device="cuda")
+        g = K.GlaStep(_dev(rows_), heads, dim, vdim, rank, tau, dim ** -0.5, 1e-5)
+        inner = torch.empty(T, rank + 3, device="cuda")
+        g.cast(inner)
+        assert torch.equal(inner[:, :rank], _dev(rows_)[:, width - rank:])
+        z = (inner[:, :rank].double() @ _dev(w_a2, torch.float64).T + _dev(b_a2, torch.float64)).float().contiguous()
+        g.decay(z)                                            # the second projection is the caller's product
         o_raw = torch.empty(T, HV, device="cuda")
         out = torch.empty(T, HV + 5, device="cuda")
-        K.gla(_dev(rows_), _dev(w_a2), _dev(b_a2), _dev(gain), alpha, o_raw, out, st, _i32(seq), _i32([0, cut[0], T]),
-              _i32(slots), heads, dim, vdim, tau, dim ** -0.5, 1e-5, True)
+        g.recur(o_raw, st, _i32(seq), _i32([0, cut[0], T]), _i32(slots), True)
+        g.finish(_dev(gain), out)
         o = out[:, :HV].cpu().numpy()
         got[0].append(o[:cut[0]]); got[1].append(o[cut[0]:])
         done = [done[i] + cut[i] for i in range(2)]
@@ -96,10 +101,11 @@ def test_gla_kernel_leaves_the_state_alone_when_told_to():
     st = _dev(rng.standard_normal((2, HD * vdim)))
     before = st.clone()
     out = torch.empty(T, HV, device="cuda")
-    K.gla(_dev(rng.standard_normal((T, 2 * HD + 2 * HV + rank))), _dev(rng.standard_normal((HD, rank))),
-          torch.zeros(HD, device="cuda"), torch.ones(vdim, device="cuda"), torch.empty(T, HD, device="cuda"),
-          torch.empty(T, HV, device="cuda"), out, st, torch.zeros(T, dtype=torch.int32, device="cuda"), _i32([0, T]),
-          _i32([1]), heads, dim, vdim, 2.0, 1.0, 1e-5, False)
+    g = K.GlaStep(_dev(rng.standard_normal((T, 2 * HD + 2 * HV + rank))), heads, dim, vdim, rank, 2.0, 1.0, 1e-5)
+    g.decay(_dev(rng.standard_normal((T, HD))))
+    g.recur(torch.empty(T, HV, device="cuda"), st, torch.zeros(T, dtype=torch.int32, device="cuda"), _i32([0, T]),
+            _i32([1]), False)
+    g.finish(torch.ones(vdim, device="cuda"), out)
     assert torch.equal(st, before) and bool(torch.isfinite(out).all())
 
 
@@ -257,6 +263,26 @@ def test_add_rows_kernel():
     xd = _dev(x)
     K.add_rows(xd, None, _dev(r))
     assert np.allclose(xd.cpu().numpy(), x + r, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_two_norms_from_one_pass(dtype):
+    """Both sublayers' norms of the same rows: the plain norm twice, and the bits of the one-output kernel."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(0)
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    for rows, width in ((1, 72), (5, 70), (300, 512), (3, 4100), (260, 2048)):
+        x = rng.standard_normal((rows, width)) * 3
+        ga, gb = rng.uniform(0.5, 1.5, width), rng.uniform(-0.5, 2.0, width)
+        a, b = torch.empty(rows, width, dtype=td, device="cuda"), torch.empty(rows, width, dtype=td, device="cuda")
+        K.rmsnorm_pair(_dev(x), _dev(ga), _dev(gb), 1e-5, a, b)
+        tol = 3e-6 if dtype == "float32" else 5e-3
+        for got, g in ((a, ga), (b, gb)):
+            want = M.rms_norm(x, g, 1e-5)
+            assert np.max(np.abs(got.float().cpu().numpy() - want)) <= tol * np.max(np.abs(want))
+            one = torch.empty(rows, width, dtype=td, device="cuda")
+            K.rmsnorm(_dev(x), _dev(g), 1e-5, one)
+            assert torch.equal(one, got)
 
 
 # ------------------------------------------------------------------------------------------ mechanisms alone
