@@ -43,7 +43,7 @@ class RotationConfig:
 
     @classmethod
     def from_reader(cls, r: KeyReader, head_dim: Optional[int]) -> "RotationConfig":
-        base, dims = r.number("base", lo=1.0), r.integer("dims", hi=1 << 14)
+        base, dims = r.number("base", lo=1.0), r.integer("dims", lo=0, hi=1 << 14)
         factor = original = fast = slow = None
         sc = r.child("scaling")
         if sc is not None:
