@@ -164,10 +164,10 @@ def mokatar_config(size, n_layers):
     win = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["dim"] ** -0.5,
            "mask": {"size": m["window"], "keep_first": m["keep"]},
            "rot": {"base": 10000.0, "dims": m["dim"] // 2,
-                   "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+                   "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     full = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["dim"] ** -0.5,
             "rot": {"base": 10000.0, "dims": m["dim"], "scaling": {"factor": 2.0}}}
-    rec = {"heads": z["heads"], "dim": m["gla_dim"], "vdim": m["gla_vdim"], "tau": 16.0, "rank": m["rank"]}
+    rec = {"heads": z["heads"], "dim": m["gla_dim"], "vdim": m["gla_vdim"], "tau": 8.0, "rank": m["rank"]}
     moe = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"]}}
     dense = {"kind": "dense", "ff": z["llama_inner"]}
     kinds = [("gla", rec), ("attention_2", full), ("gla", rec), ("attention", win)]
@@ -175,7 +175,7 @@ def mokatar_config(size, n_layers):
               for i in range(n_layers)]
     return MokatarConfig.from_dict({
         "architecture": "Mokatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0,
-        "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+        "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 29, "mul_cur": 19}},
         "layers": layers, "loop": {"start": 0, "stop": n_layers, "times": 1}})
 
 

@@ -74,7 +74,7 @@ MOK_WINDOWED = config([layer("attention", windowed(heads=4, kv=2, dim=16, vdim=1
 MOK_BIASED = config([layer("attention_2", biased(heads=4, kv=2, dim=16, vdim=8, rot=16))], width=64)
 MOK_GLA = config([layer("gla", gla(heads=4, dim=8, vdim=16, tau=4.0, rank=6))], width=64)
 MOK_MOE = config([layer("gla", gla(heads=1, dim=8, vdim=8, tau=4.0, rank=2), moe(experts=12, top=4))], width=64)
-MOK_DENSE = config([layer("gla", gla(heads=1, dim=8, vdim=8, tau=4.0, rank=2), dense(136))], width=64)
+MOK_DENSE = config([layer("gla", gla(heads=1, dim=8, vdim=8, tau=4.0, rank=2), dense(120))], width=64)
 MOK_LOOP = config([layer("gla", gla(heads=2, dim=8, vdim=8, tau=4.0, rank=2)),
                    layer("attention_2", biased(heads=2, kv=2, dim=8, vdim=8, rot=4))], width=64, loop=(0, 2, 4))
 

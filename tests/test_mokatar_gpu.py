@@ -212,7 +212,7 @@ def test_pair_embedding_kernel_and_its_state():
     ref = np.stack([want(None, 4), want(4, 5), want(5, 6), want(41, 7)])
     assert np.max(np.abs(got - ref)) <= 1e-6 * np.max(np.abs(ref))
     assert last.flatten().tolist() == [7, 41, 41, 6, 41]
-    # step 2: one token each (the order of the sequences turned round), and a row of no sequence
+    # step 2: one token each (the sequences in the other order), and a row of no sequence
     got = run([8, 9, 3], [10, 3, 0], [0, 1, -1], [0, 1, 2, 3], [0, 3, 4])
     ref = np.stack([want(7, 8), want(6, 9), want(None, 3)])
     assert np.max(np.abs(got - ref)) <= 1e-6 * np.max(np.abs(ref))
@@ -689,7 +689,7 @@ def test_the_token_in_front_across_a_steps_border(dtype, tmp_path):
     the plain implementation says, in a batch of two requests and in a slot used before."""
     from stratum_b200.engine import StepEntry
     cfg_raw = config([layer("gla", gla(heads=1, dim=8, vdim=8, tau=4.0, rank=2), dense(40))], vocab=60, width=48,
-                     emb_scale=0.05, buckets=997, mul_prev=31, mul_cur=17)
+                     emb_scale=0.05, buckets=997, mul_prev=29, mul_cur=19)
     path, cfg, w = make(str(tmp_path / "pairs"), None, dtype, seed=8, cfg=cfg_raw)
     a, b = [3, 9, 27, 21, 5, 11], [3, 9, 28, 21, 5, 11]
     other = [40, 41, 42, 43]
