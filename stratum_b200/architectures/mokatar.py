@@ -79,8 +79,9 @@ def describe_mokatar(cfg: MokatarConfig) -> ModelSpec:
         schedule.append(ScheduleEntry(i))
     b = cfg.bigram
     embedding = PartSpec("pair_embedding", {
-        "vocab": cfg.vocab, "hidden": cfg.width, "tensor": "embed", "pairs": "bigram", "buckets": b.buckets,
-        "mul_prev": b.mul_prev, "mul_cur": b.mul_cur, "scale": cfg.embedding_scale})
+        "vocab": cfg.vocab, "hidden": cfg.width, "tensor": "embed", "pairs": "bigram" if b is not None else None,
+        "buckets": b.buckets if b else 0, "mul_prev": b.mul_prev if b else 0, "mul_cur": b.mul_cur if b else 0,
+        "scale": cfg.embedding_scale})
     return ModelSpec(
         hidden=cfg.width, vocab=cfg.vocab, embedding=embedding, layers=tuple(layers), schedule=tuple(schedule),
         final_norm=norm("final.norm", cfg.logit_scale),

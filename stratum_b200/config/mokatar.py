@@ -1,7 +1,8 @@
 """MokatarConfig: the sizes and constants of a Mokatar decoder, read from config.json.
 
 A Mokatar config.json names its architecture under "architecture", gives "vocab", "width", "norm": {"eps"},
-"logit_scale", "embedding": {"scale", "bigram": {"buckets", "mul_prev", "mul_cur"}} and lists its layers one by one:
+"logit_scale", "embedding": {"scale", "bigram": {"buckets", "mul_prev", "mul_cur"}} (a file without "bigram" has no
+pair table) and lists its layers one by one:
 each entry gives the mixer's kind ("type": "attention", "attention_2" or "gla"), the mixer's sizes and constants
 ("mixer") and its feed-forward ("mlp": dense, a mixture of experts, or null for a layer that is a mixer alone).
 "loop": {"start", "stop", "times"} makes the layers start .. stop - 1 run `times` times in a row with the same
@@ -85,10 +86,8 @@ class AttentionMixerConfig:
         dim, vdim = r.integer("dim", hi=1 << 14), r.integer("vdim", hi=1 << 14)
         scale = r.number("scale", lo=0.0)
         rr = r.child("rot")
-        rot = None
-        if rr is None:
-            r.problems.append("missing required key 'rot'")
-        else:
+        rot = None                   # a mixer without "rot" rotates nothing
+        if rr is not None:
             rot = RotationConfig.from_reader(rr, dim)
             r.adopt(rr)
         window = keep = 0
@@ -102,8 +101,9 @@ class AttentionMixerConfig:
         return cls(heads, kv, dim, vdim, scale, rot, window or 0, keep or 0)
 
     def to_dict(self) -> Dict[str, Any]:
-        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-             "rot": self.rot.to_dict()}
+        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.rot is not None:
+            d["rot"] = self.rot.to_dict()
         if self.window:
             d["mask"] = {"size": self.window, "keep_first": self.keep_first}
         return d
@@ -198,7 +198,7 @@ class MokatarConfig(ModelConfig):
     eps: float
     logit_scale: float
     embedding_scale: float
-    bigram: BigramConfig
+    bigram: Optional[BigramConfig]
     layers: Tuple[MokatarLayer, ...]
     loop: Optional[LoopConfig] = None
     torch_dtype: str = "bfloat16"
@@ -229,15 +229,11 @@ class MokatarConfig(ModelConfig):
         else:
             r.adopt(norm)
         emb = r.child("embedding")
-        emb_scale, bigram = 1.0, None
-        if emb is None:
-            r.problems.append("missing required key 'embedding'")
-        else:
+        emb_scale, bigram = 1.0, None        # without "bigram" the embedding is the token table's row times the scale
+        if emb is not None:
             emb_scale = emb.number("scale", default=1.0)
             bg = emb.child("bigram")
-            if bg is None:
-                emb.problems.append("missing required key 'bigram'")
-            else:
+            if bg is not None:
                 buckets = bg.integer("buckets", hi=1 << 30)
                 # the products previous * mul_prev + token * mul_cur are formed in 64 bits on the device
                 mp, mc = bg.integer("mul_prev", lo=0, hi=1 << 30), bg.integer("mul_cur", lo=0, hi=1 << 30)
@@ -303,8 +299,10 @@ class MokatarConfig(ModelConfig):
     def to_dict(self) -> Dict[str, Any]:
         d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
              "norm": {"eps": self.eps}, "logit_scale": self.logit_scale,
-             "embedding": {"scale": self.embedding_scale, "bigram": self.bigram.to_dict()},
+             "embedding": {"scale": self.embedding_scale},
              "layers": [layer.to_dict() for layer in self.layers], "torch_dtype": self.torch_dtype}
+        if self.bigram is not None:
+            d["embedding"]["bigram"] = self.bigram.to_dict()
         if self.loop is not None:
             d["loop"] = self.loop.to_dict()
         return d

@@ -41,6 +41,7 @@ STRATUM_EXPORT int stratum_embed_gather(const void* table, int dtype, const int*
 // cache slot); the thread that reads it then stores the sequence's last token of this step there, so the entry is
 // read before it is rewritten.  Tokens of no sequence (sequence index -1) read row `buckets` and touch no state.
 // out2, where given, receives the same rows (a model that adds the embedded tokens to its stream again later).
+// Without a pair table (pairs null) the rows are table[ids[t]] * scale and no state is read or written.
 struct EmbedPairs {
   const void* table;        // [vocab][hidden]
   const void* pairs;        // [buckets + 1][hidden]
@@ -65,7 +66,7 @@ __global__ void embed_pairs_kernel(const EmbedPairs P) {
   const int t = blockIdx.x;
   int id = P.ids[t];
   if (id < 0 || id >= P.vocab) id = 0;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && P.pairs) {
     const int seq = P.token_seq[t];
     int prev = -1;
     if (seq >= 0) {
@@ -80,11 +81,11 @@ __global__ void embed_pairs_kernel(const EmbedPairs P) {
   }
   __syncthreads();
   const T* a = (const T*)P.table + (size_t)id * P.hidden;
-  const T* b = (const T*)P.pairs + (size_t)row_s * P.hidden;
+  const T* b = P.pairs ? (const T*)P.pairs + (size_t)row_s * P.hidden : nullptr;
   float* o = P.out + (size_t)t * P.hidden;
   float* o2 = P.out2 ? P.out2 + (size_t)t * P.hidden : nullptr;
   for (int i = threadIdx.x; i < P.hidden; i += blockDim.x) {
-    const float v = fmaf(to_float(a[i]), P.scale, to_float(b[i]));
+    const float v = b ? fmaf(to_float(a[i]), P.scale, to_float(b[i])) : to_float(a[i]) * P.scale;
     o[i] = v;
     if (o2) o2[i] = v;
   }
@@ -93,7 +94,8 @@ __global__ void embed_pairs_kernel(const EmbedPairs P) {
 STRATUM_EXPORT int stratum_embed_pairs(const EmbedPairs* params, int dtype, cudaStream_t stream) {
   const EmbedPairs& P = *params;
   if (P.n_tokens <= 0) return 0;
-  if (P.buckets < 1 || P.hidden < 1 || P.vocab < 1 || P.mul_prev < 0 || P.mul_cur < 0) return STRATUM_ERR_SHAPE;
+  if ((P.pairs && (P.buckets < 1 || !P.last)) || P.hidden < 1 || P.vocab < 1 || P.mul_prev < 0 || P.mul_cur < 0)
+    return STRATUM_ERR_SHAPE;
   const int threads = P.hidden >= 1024 ? 256 : 128;
   if (dtype == STRATUM_DT_F32) launch_pdl(embed_pairs_kernel<float>, P.n_tokens, threads, 0, stream, P);
   else if (dtype == STRATUM_DT_BF16) launch_pdl(embed_pairs_kernel<bf16>, P.n_tokens, threads, 0, stream, P);

@@ -161,30 +161,35 @@ class _EmbedPairs(ctypes.Structure):
                 ("scale", c_float), ("reserved2", c_float)]
 
 
-def embed_pairs(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, token_pos: torch.Tensor,
-                token_seq: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, last: torch.Tensor,
+def embed_pairs(table: torch.Tensor, pairs: Optional[torch.Tensor], ids: torch.Tensor, token_pos: torch.Tensor,
+                token_seq: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, last: Optional[torch.Tensor],
                 out: torch.Tensor, out2: Optional[torch.Tensor], scale: float, mul_prev: int, mul_cur: int,
                 write_state: bool = True) -> None:
     """out[t] = table[ids[t]] * scale + pairs[(prev * mul_prev + ids[t] * mul_cur) mod buckets], float32; prev is the
     token in front of t in its sequence (from the step, or from `last`, int32 [slots, 1], which then takes the
     sequence's last token of this step); a sequence's first token reads the last row of pairs [buckets + 1, hidden].
-    out2 (or None) receives the same rows."""
-    _need(table, "table"); _need(pairs, "pairs", table.dtype); _need(ids, "ids", torch.int32)
+    out2 (or None) receives the same rows.  pairs None: out[t] = table[ids[t]] * scale, and `last` is not touched."""
+    _need(table, "table"); _need(ids, "ids", torch.int32)
     _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
     _need(seq_start, "seq_start", torch.int32); _need(seq_slot, "seq_slot", torch.int32)
-    _need(last, "last", torch.int32); _need(out, "out", torch.float32)
-    if pairs.shape[1] != table.shape[1] or out.shape != (ids.numel(), table.shape[1]) or pairs.shape[0] < 2:
+    _need(out, "out", torch.float32)
+    if out.shape != (ids.numel(), table.shape[1]):
         raise KernelError("embed_pairs: shapes disagree")
     p = _EmbedPairs()
-    p.table, p.pairs, p.ids, p.token_pos = table.data_ptr(), pairs.data_ptr(), ids.data_ptr(), token_pos.data_ptr()
+    p.table, p.ids, p.token_pos = table.data_ptr(), ids.data_ptr(), token_pos.data_ptr()
     p.token_seq, p.seq_start, p.seq_slot = token_seq.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr()
-    p.last, p.out = last.data_ptr(), out.data_ptr()
+    p.out = out.data_ptr()
+    if pairs is not None:
+        _need(pairs, "pairs", table.dtype); _need(last, "last", torch.int32)
+        if pairs.shape[1] != table.shape[1] or pairs.shape[0] < 2:
+            raise KernelError("embed_pairs: shapes disagree")
+        p.pairs, p.last, p.buckets = pairs.data_ptr(), last.data_ptr(), pairs.shape[0] - 1
     if out2 is not None:
         _need(out2, "out2", torch.float32)
         if out2.shape != out.shape:
             raise KernelError("embed_pairs: out2 and out disagree")
         p.out2 = out2.data_ptr()
-    p.n_tokens, p.hidden, p.vocab, p.buckets = ids.numel(), table.shape[1], table.shape[0], pairs.shape[0] - 1
+    p.n_tokens, p.hidden, p.vocab = ids.numel(), table.shape[1], table.shape[0]
     p.mul_prev, p.mul_cur, p.write_state, p.scale = int(mul_prev), int(mul_cur), int(bool(write_state)), float(scale)
     f = _fn("elementwise", "stratum_embed_pairs", [c_void_p, c_int, c_void_p])
     _check(f(ctypes.addressof(p), dtype_code(table.dtype), _stream()), "embed_pairs")

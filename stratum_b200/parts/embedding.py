@@ -58,32 +58,35 @@ class PairEmbedding(Embedding):
     reads the last row of `pairs` ([buckets + 1, hidden]).  The token in front of a step's first token is part of what
     a sequence keeps between steps: one int per sequence in a state block of the cache, read and rewritten by the
     kernel that gathers the rows, so that a decode step whose token ids are fed on the device needs nothing from the
-    host.  params: vocab, hidden, tensor (the table's name), pairs (the pair table's name), buckets, mul_prev,
-    mul_cur, scale."""
+    host.  params: vocab, hidden, tensor (the table's name), pairs (the pair table's name; None: no pair table, the
+    rows are the token table's times the scale and nothing is kept), buckets, mul_prev, mul_cur, scale."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.name = spec.get("tensor") or self.prefix + "weight"
-        self.pairs_name = str(spec["pairs"])
+        self.pairs_name = spec.get("pairs")
         self.buckets, self.mul_prev, self.mul_cur = int(spec["buckets"]), int(spec["mul_prev"]), int(spec["mul_cur"])
         self.scale = float(spec.get("scale", 1.0))
         self._table: Optional[torch.Tensor] = None
         self._pairs: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.vocab, self.hidden)),
-                self.pairs_name: TensorSpec((self.buckets + 1, self.hidden))}
+        t = {self.name: TensorSpec((self.vocab, self.hidden))}
+        if self.pairs_name:
+            t[self.pairs_name] = TensorSpec((self.buckets + 1, self.hidden))
+        return t
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
-        self._table, self._pairs = weights[self.name], weights[self.pairs_name]
+        self._table = weights[self.name]
+        self._pairs = weights[self.pairs_name] if self.pairs_name else None
 
     def table(self) -> torch.Tensor:
         return self._table
 
-    def cache_spec(self) -> StateSpec:
-        return StateSpec((1,), "int32")
+    def cache_spec(self) -> Optional[StateSpec]:
+        return StateSpec((1,), "int32") if self.pairs_name else None
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         raise ValueError("pair_embedding needs the step and its state: forward_step")

@@ -53,19 +53,23 @@ def rms_norm(x, gain, eps, one_plus=False):
 
 # ---------------------------------------------------------------------------------------------- embedding
 def embed(cfg, W, tokens):
-    e = cfg["embedding"]
-    big = e["bigram"]
-    table, pairs = np.asarray(W["embed"], F64), np.asarray(W["bigram"], F64)
+    e = cfg.get("embedding") or {}
+    big, scale = e.get("bigram"), e.get("scale", 1.0)
+    table = np.asarray(W["embed"], F64)
     out = np.zeros((len(tokens), table.shape[1]), F64)
     for i, tok in enumerate(tokens):
-        row = big["buckets"] if i == 0 else (tokens[i - 1] * big["mul_prev"] + tok * big["mul_cur"]) % big["buckets"]
-        out[i] = table[tok] * e["scale"] + pairs[row]
+        out[i] = table[tok] * scale
+        if big is not None:                   # a model without a pair table adds nothing
+            row = big["buckets"] if i == 0 else (tokens[i - 1] * big["mul_prev"] + tok * big["mul_cur"]) % big["buckets"]
+            out[i] += np.asarray(W["bigram"][row], F64)
     return out
 
 
 # ---------------------------------------------------------------------------------------------- rotation
 def frequencies(rot):
-    """(f [dims / 2], magnitude of cos and sin) of a mixer's `rot` object."""
+    """(f [dims / 2], magnitude of cos and sin) of a mixer's `rot` object; none at all: nothing is turned."""
+    if not rot or not rot.get("dims"):
+        return np.zeros(0, F64), 1.0
     n, base = rot["dims"], float(rot["base"])
     f = np.array([base ** (-2.0 * i / n) for i in range(n // 2)], F64)
     sc = rot.get("scaling") or {}
@@ -129,7 +133,7 @@ def attention(m, W, pre, h, eps, positions=None):
     k = linear(h, W[pre + "k"]).reshape(T, G, d)
     v = linear(h, W[pre + "v"]).reshape(T, G, dv)
     q, k = rms_norm(q, W[pre + "q.norm"], eps), rms_norm(k, W[pre + "k.norm"], eps)
-    f, mag = frequencies(m["rot"])
+    f, mag = frequencies(m.get("rot"))
     q, k = rotate(q, p, f, mag, True), rotate(k, p, f, mag, True)
     mask = m.get("mask") or {}
     o = masked_softmax_attention(q, k, v, m["scale"], np.asarray(W[pre + "sink"], F64), mask.get("size", 0),
@@ -144,7 +148,7 @@ def attention_2(m, W, pre, h, eps, positions=None):
     q = rms_norm(linear(h, W[pre + "q"], W[pre + "q.b"]), W[pre + "q.norm"], eps).reshape(T, H, d)
     k = rms_norm(linear(h, W[pre + "k"], W[pre + "k.b"]), W[pre + "k.norm"], eps).reshape(T, G, d)
     v = linear(h, W[pre + "v"], W[pre + "v.b"]).reshape(T, G, dv)
-    f, mag = frequencies(m["rot"])
+    f, mag = frequencies(m.get("rot"))
     q, k = rotate(q, p, f, mag, False), rotate(k, p, f, mag, False)
     o = masked_softmax_attention(q, k, v, m["scale"], np.zeros(H, F64), 0, 0)
     return linear(o.reshape(T, H * dv), W[pre + "o"])

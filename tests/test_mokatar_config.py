@@ -30,6 +30,27 @@ def test_configuration_round_trip_and_registry():
     assert (a.logit_scale, a.embedding_scale, a.bigram.buckets) == (0.7, 3.0, 53)
 
 
+def test_what_a_file_does_not_mention_does_not_exist():
+    """No pair table, no rotation, no window, no loop, no feed-forward: each is left out by leaving its key out."""
+    from stratum_b200.config import find_architecture
+    from stratum_b200.engine.model import Model
+    raw = copy.deepcopy(MOK_A)
+    del raw["embedding"]["bigram"]
+    del raw["layers"][0]["mixer"]["rot"]
+    del raw["layers"][0]["mixer"]["mask"]
+    del raw["layers"][2]["mixer"]["rot"]["scaling"]
+    del raw["loop"]
+    del raw["logit_scale"]
+    cfg = _cfg(raw)
+    assert cfg.bigram is None and cfg.loop is None and cfg.logit_scale == 1.0
+    assert cfg.layers[0].mixer.rot is None and cfg.layers[0].mixer.window == 0 and cfg.layers[2].mixer.rot.factor is None
+    assert type(cfg).from_dict(cfg.to_dict()) == cfg
+    model = Model(find_architecture(raw).describe_model(cfg), None)
+    assert "bigram" not in model.tensors() and "loop.step" not in model.tensors()
+    assert len(model.cache_specs()) == len(model.schedule) == 4          # nothing kept for the embedding
+    assert model.layers[0].part("mixer").position is None
+
+
 def test_configuration_problems_are_listed_together():
     from stratum_b200.config import ConfigError
     raw = copy.deepcopy(MOK_A)

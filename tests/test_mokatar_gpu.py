@@ -301,6 +301,30 @@ def test_each_mechanism_alone(name, dtype, tmp_path):
         assert_close(got, plain_logits(cfg, w, toks), dtype, f"{name} n={n}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_model_without_pair_table_rotation_window_and_loop(dtype, tmp_path):
+    """What a file does not mention does not exist: the same layers with those keys left out."""
+    import copy
+    from mokatar_helpers import MOK_A
+    from stratum_b200.engine import StepEntry
+    raw = copy.deepcopy(MOK_A)
+    del raw["embedding"]["bigram"]
+    del raw["layers"][0]["mixer"]["rot"]
+    del raw["layers"][0]["mixer"]["mask"]
+    del raw["layers"][2]["mixer"]["rot"]["scaling"]
+    del raw["loop"]
+    path, cfg, w = make(str(tmp_path / "bare"), None, dtype, seed=12, cfg=raw)
+    assert "bigram" not in w
+    engine = _engine(path, dtype)
+    toks = clear_tokens(np.random.default_rng(0), 90, cfg, w, dtype)
+    ref = plain_logits(cfg, w, toks)
+    slot = engine.acquire()
+    got = engine.step([StepEntry(slot, toks[:70], list(range(70)))]).cpu().numpy()
+    got = np.concatenate([got] + [engine.step([StepEntry(slot, [t], [0])]).cpu().numpy() for t in toks[70:]])
+    engine.release(slot)
+    assert_close(got, ref, dtype, "a bare model")
+
+
 def test_the_stream_after_every_layer_run(tmp_path):
     """float32: the residual stream behind every stop of the schedule that is a layer, looped passes included."""
     from stratum_b200.engine import StepEntry
